@@ -1,6 +1,7 @@
 """Typed model configuration and the architecture registry.
 
-A model folder's ``config.json`` names its architecture in ``architectures[0]``.
+A model folder's ``config.json`` names its architecture in ``architectures[0]`` (or, in formats
+that name exactly one, in the string ``architecture``).
 The registry maps that name to an :class:`ArchEntry`: how to parse the typed
 configuration and how to build the model from it.  Lookup of an unknown name
 fails with an error that lists the supported names, in the manner of the
@@ -69,10 +70,14 @@ def read_config_json(model_dir: str) -> Dict[str, Any]:
 
 
 def arch_name_of(raw: Dict[str, Any]) -> str:
+    """The architecture's name: ``architectures[0]``, or the string ``architecture`` of formats that name one."""
     names = raw.get("architectures")
-    if not isinstance(names, list) or not names or not isinstance(names[0], str):
-        raise ConfigError("config.json: missing key: architectures")
-    return names[0]
+    if isinstance(names, list) and names and isinstance(names[0], str):
+        return names[0]
+    one = raw.get("architecture")
+    if isinstance(one, str) and one:
+        return one
+    raise ConfigError("config.json: missing key: architectures")
 
 
 def load_config(model_dir: str):

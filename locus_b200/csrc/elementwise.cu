@@ -450,3 +450,90 @@ extern "C" int locus_gather_rows(const void* src, int dt, const int* idx, int di
     }
     return locus_launch_status();
 }
+
+// ---------------------------------------------------------------------------
+// Rows of the float32 residual stream in another element type: out[i, :] = x[i, :] (a sublayer that
+// reads the stream itself, without a norm in front of it, takes its rounding to the model's type).
+template <typename TO>
+__global__ void __launch_bounds__(256) cast_rows_kernel(const float* __restrict__ x, TO* __restrict__ out,
+                                                        long long n4, long long n) {
+    pdl_entry();
+    pdl_trigger();
+    const long long i = static_cast<long long>(blockIdx.x) * blockDim.x + threadIdx.x;
+    if (i < n4) {
+        const float4 v = reinterpret_cast<const float4*>(x)[i];
+        put4(out + 4 * i, v.x, v.y, v.z, v.w);
+    }
+    if (i == 0)
+        for (long long j = 4 * n4; j < n; ++j) out[j] = from_f<TO>(x[j]);
+}
+
+extern "C" int locus_cast_rows(const float* x, void* out, int out_dt, long long n, cudaStream_t stream) {
+    if (n <= 0) return 0;
+    if ((reinterpret_cast<uintptr_t>(x) | reinterpret_cast<uintptr_t>(out)) & 15) return LOCUS_ERR_UNSUPPORTED;
+    const long long n4 = n / 4;
+    const long long blocks = (n4 > 0 ? n4 : 1) / 256 + 1;
+    if (blocks > 0x7fffffffLL) return LOCUS_ERR_UNSUPPORTED;
+    if (out_dt == LOCUS_DT_BF16)
+        locus_launch(cast_rows_kernel<bf16>, static_cast<int>(blocks), 256, 0, stream, x, static_cast<bf16*>(out), n4, n);
+    else if (out_dt == LOCUS_DT_F32)
+        locus_launch(cast_rows_kernel<float>, static_cast<int>(blocks), 256, 0, stream, x, static_cast<float*>(out), n4, n);
+    else
+        return LOCUS_ERR_UNSUPPORTED;
+    return locus_launch_status();
+}
+
+// ---------------------------------------------------------------------------
+// The norm of a sublayer's OUTPUT, added to the residual stream: x[i, :] += y[i, :] * rsqrt(mean(y[i]^2) + eps) * w
+// (y and x float32, statistics float32, the sum of squares in an order that depends on H only).  One block per
+// row; a row of up to 4096 elements stays in registers between the two passes.
+template <typename TW>
+__global__ void __launch_bounds__(256) rmsnorm_add_kernel(const float* __restrict__ y, const TW* __restrict__ w,
+                                                          float eps, float* __restrict__ x, int H) {
+    __shared__ float warp_part[8];
+    __shared__ float scale_s;
+    pdl_entry();
+    pdl_trigger();
+    const size_t base = static_cast<size_t>(blockIdx.x) * H;
+    float v[16];
+    float ss = 0.f;
+#pragma unroll
+    for (int u = 0; u < 16; ++u) {
+        const int j = threadIdx.x + u * 256;
+        v[u] = j < H ? y[base + j] : 0.f;
+        ss = fmaf(v[u], v[u], ss);
+    }
+    for (int j = threadIdx.x + 4096; j < H; j += 256) {
+        const float t = y[base + j];
+        ss = fmaf(t, t, ss);
+    }
+    ss = warp_sum(ss);
+    if ((threadIdx.x & 31) == 0) warp_part[threadIdx.x >> 5] = ss;
+    __syncthreads();
+    if (threadIdx.x == 0) {
+        float tot = 0.f;
+        for (int k = 0; k < 8; ++k) tot += warp_part[k];
+        scale_s = 1.0f / sqrtf(tot / static_cast<float>(H) + eps);
+    }
+    __syncthreads();
+    const float scale = scale_s;
+#pragma unroll
+    for (int u = 0; u < 16; ++u) {
+        const int j = threadIdx.x + u * 256;
+        if (j < H) x[base + j] += v[u] * scale * to_f(w[j]);
+    }
+    for (int j = threadIdx.x + 4096; j < H; j += 256) x[base + j] += y[base + j] * scale * to_f(w[j]);
+}
+
+extern "C" int locus_rmsnorm_add(const float* y, const void* w, int w_dt, float eps, float* x, int n_rows, int H,
+                                 cudaStream_t stream) {
+    if (n_rows <= 0) return 0;
+    if (H <= 0) return LOCUS_ERR_UNSUPPORTED;
+    if (w_dt == LOCUS_DT_BF16)
+        locus_launch(rmsnorm_add_kernel<bf16>, n_rows, 256, 0, stream, y, static_cast<const bf16*>(w), eps, x, H);
+    else if (w_dt == LOCUS_DT_F32)
+        locus_launch(rmsnorm_add_kernel<float>, n_rows, 256, 0, stream, y, static_cast<const float*>(w), eps, x, H);
+    else
+        return LOCUS_ERR_UNSUPPORTED;
+    return locus_launch_status();
+}

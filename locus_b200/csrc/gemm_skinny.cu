@@ -28,6 +28,7 @@ struct SkinnyArgs {
     void* out;
     int out_dt;
     int accumulate;
+    int act;  // 1: relu(v)^2 after the bias, before the row scale
     const float* row_scale;
     const int* scale_rows;
     const int* x_rows;
@@ -196,6 +197,10 @@ __global__ void __launch_bounds__(32 * SK_WARPS, ROUTE ? 1 : (NT == 1 ? 4 : ((NT
         }
         if (DUAL) v = v / (1.0f + expf(-v)) * u;
         if (a.bias) v += ld_dyn(a.bias, a.bias_dt, n);
+        if (a.act == 1) {
+            v = fmaxf(v, 0.f);
+            v *= v;
+        }
         const int row = tok0 + t;
         if (a.row_scale) v *= a.row_scale[a.scale_rows ? a.scale_rows[row] : row];
         const size_t o = static_cast<size_t>(row) * a.ldo + n;
@@ -251,12 +256,14 @@ static int launch(const SkinnyArgs& a, int tiles, bool dual, cudaStream_t stream
 // tile_tokens: 8, 16 or 32 rows of x per tile (for a grouped product: the tile size of the
 // tile list).  x and W bfloat16; K a multiple of 8; 16-byte aligned rows.
 extern "C" int locus_gemm_skinny(const void* x, const void* w, const void* w2, const void* bias, int bias_dt,
-                                 void* out, int out_dt, int accumulate, const float* row_scale,
+                                 void* out, int out_dt, int flags, const float* row_scale,
                                  const int* scale_rows, const int* x_rows, int x_row_div, int M, int N, int K,
                                  long long ldx, long long ldo, int tile_tokens, const int* tile_expert,
                                  const int* tile_row0, const int* tile_rows, const int* n_tiles, int max_tiles,
                                  long long w_expert_stride, int lists_ready, cudaStream_t stream) {
     if (N <= 0 || K <= 0 || K % 8 != 0 || ldx % 8 != 0) return LOCUS_ERR_UNSUPPORTED;
+    const int accumulate = flags & 1, act = (flags >> 1) & 1;  // bit 0: add into out; bit 1: squared ReLU
+    if (act && w2 != nullptr) return LOCUS_ERR_UNSUPPORTED;
     if ((reinterpret_cast<uintptr_t>(x) | reinterpret_cast<uintptr_t>(w) | reinterpret_cast<uintptr_t>(w2)) & 15)
         return LOCUS_ERR_UNSUPPORTED;
     if (accumulate && out_dt != LOCUS_DT_F32) return LOCUS_ERR_UNSUPPORTED;
@@ -264,7 +271,7 @@ extern "C" int locus_gemm_skinny(const void* x, const void* w, const void* w2, c
     if (tile_tokens != 8 && tile_tokens != 16 && tile_tokens != 32) return LOCUS_ERR_UNSUPPORTED;
     SkinnyArgs a;
     a.x = static_cast<const bf16*>(x); a.w = static_cast<const bf16*>(w); a.w2 = static_cast<const bf16*>(w2);
-    a.bias = bias; a.bias_dt = bias_dt; a.out = out; a.out_dt = out_dt; a.accumulate = accumulate;
+    a.bias = bias; a.bias_dt = bias_dt; a.out = out; a.out_dt = out_dt; a.accumulate = accumulate; a.act = act;
     a.row_scale = row_scale; a.scale_rows = scale_rows; a.x_rows = x_rows; a.x_row_div = x_row_div;
     a.M = M; a.N = N; a.K = K; a.ldx = ldx; a.ldo = ldo; a.tile_expert = tile_expert; a.tile_row0 = tile_row0;
     a.tile_rows = tile_rows; a.n_tiles = n_tiles; a.w_expert_stride = w_expert_stride;
@@ -281,13 +288,14 @@ extern "C" int locus_gemm_skinny(const void* x, const void* w, const void* w2, c
 // w_all by the kernel above -- the same kernel, and the same order of every sum, as locus_gemm_skinny gives for any
 // number of tokens -- and in its last block the selection (locus_router_select) and the expert layout
 // (locus_moe_sort) of route_select.cuh.  T <= 16 tokens (one row tile), T * k <= RS_MAX_PAIRS, E <= RS_MAX_E.
-// counter: one int, zero before the call and zero after it.
+// counter: one int, zero before the call and zero after it.  logit_bias (or null): float32 [rows of w_all], added to
+// the logits before anything is chosen (a router with a bias of its own; it enters selection and weights alike).
 extern "C" int locus_router_fused_small(const void* h, const void* w_all, float* logits, int ld, int* counter, int* ids,
                                         float* wts, float* gamma, int T, int H, long long ldh, int E, int k, int has_gate,
                                         int renorm, float scale, int score_fn, const float* sel_bias, int n_group,
                                         int n_group_used, int tile_m, int* counts, int* offsets, int* sorted_pair,
                                         int* pair_pos, int* tile_expert, int* tile_row0, int* tile_rows, int* n_tiles,
-                                        cudaStream_t stream) {
+                                        const float* logit_bias, cudaStream_t stream) {
     if (T <= 0) return 0;
     const RouteOpts o{k, renorm, score_fn, n_group, n_group_used, scale, sel_bias};
     const int n_rows = E + (has_gate ? 1 : 0);
@@ -297,7 +305,7 @@ extern "C" int locus_router_fused_small(const void* h, const void* w_all, float*
     if ((reinterpret_cast<uintptr_t>(h) | reinterpret_cast<uintptr_t>(w_all)) & 15) return LOCUS_ERR_UNSUPPORTED;
     SkinnyArgs a;
     a.x = static_cast<const bf16*>(h); a.w = static_cast<const bf16*>(w_all); a.w2 = nullptr;
-    a.bias = nullptr; a.bias_dt = 0; a.out = logits; a.out_dt = LOCUS_DT_F32; a.accumulate = 0;
+    a.bias = logit_bias; a.bias_dt = LOCUS_DT_F32; a.out = logits; a.out_dt = LOCUS_DT_F32; a.accumulate = 0; a.act = 0;
     a.row_scale = nullptr; a.scale_rows = nullptr; a.x_rows = nullptr; a.x_row_div = 1;
     a.M = T; a.N = n_rows; a.K = H; a.ldx = ldh; a.ldo = ld; a.tile_expert = nullptr; a.tile_row0 = nullptr;
     a.tile_rows = nullptr; a.n_tiles = nullptr; a.w_expert_stride = 0; a.lists_ready = 0;

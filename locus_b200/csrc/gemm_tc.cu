@@ -62,6 +62,7 @@ struct TileGeom {
 struct TcArgs {
     int M, N, K, TN, dual, stages, tmem_cols, tiles_x, tiles_y, acc_bufs;
     int accumulate;
+    int act;  // 1: relu(v)^2 after the bias, before the row scale (never with a product split along K)
     void* out;
     int out_dt;
     long long ldo;
@@ -435,6 +436,10 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant_
                         x = __fdividef(g, 1.0f + __expf(-g)) * __uint_as_float(u[j]);
                     }
                     x += bias;
+                    if (a.act == 1) {
+                        x = fmaxf(x, 0.f);
+                        x *= x;
+                    }
                     if (a.row_scale) x *= scales[c0 + j];
                     val[j] = x;
                 }
@@ -596,11 +601,13 @@ static int pow2_at_least(int v) {
 // kernel adds them in order and does the epilogue.  The splits are renumbered so that none is empty.
 extern "C" int locus_gemm_tc(const void* x, long long x_rows_total, long long ldx, const void* w, const void* w2,
                              long long w_rows_total, const void* bias, int bias_dt, void* out, int out_dt,
-                             int accumulate, const float* row_scale, const int* scale_rows, int M, int N, int K,
+                             int flags, const float* row_scale, const int* scale_rows, int M, int N, int K,
                              long long ldo, int TN, const int* tile_expert, const int* tile_row0,
                              const int* tile_rows, const int* n_tiles, int max_tiles, float* split_scratch,
                              int splits, cudaStream_t stream) {
     const int dual = w2 != nullptr ? 1 : 0;
+    const int accumulate = flags & 1, act = (flags >> 1) & 1;  // bit 0: add into out; bit 1: squared ReLU
+    if (act && (dual || splits > 1)) return LOCUS_ERR_UNSUPPORTED;
     if (N <= 0 || K <= 0 || K % 8 != 0 || ldx % 8 != 0) return LOCUS_ERR_UNSUPPORTED;
     if (TN < 16 || TN > 256 || TN % 16 != 0 || (dual && TN > 256)) return LOCUS_ERR_UNSUPPORTED;
     if ((reinterpret_cast<uintptr_t>(x) | reinterpret_cast<uintptr_t>(w) | reinterpret_cast<uintptr_t>(w2)) & 15)
@@ -654,6 +661,7 @@ extern "C" int locus_gemm_tc(const void* x, long long x_rows_total, long long ld
     }
     const bool split = a.splits > 1;
     a.accumulate = split ? 0 : accumulate;
+    a.act = act;
     a.out = split ? split_scratch : out;
     a.out_dt = split ? LOCUS_DT_F32 : out_dt;
     a.ldo = split ? N : ldo;

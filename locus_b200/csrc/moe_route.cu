@@ -44,7 +44,8 @@ template <typename TX, typename TW>
 __global__ void __launch_bounds__(256) router_topk_kernel(
     const TX* __restrict__ h, const TW* __restrict__ wr, const void* __restrict__ wg, int wg_dt,
     float* __restrict__ logits, int* __restrict__ counters, int* __restrict__ ids,
-    float* __restrict__ wts, float* __restrict__ gamma, int T, int H, int E, const RouteOpts o) {
+    float* __restrict__ wts, float* __restrict__ gamma, int T, int H, int E, const RouteOpts o,
+    const float* __restrict__ logit_bias) {
     extern __shared__ __align__(16) unsigned char smem_raw[];
     TX* hs = reinterpret_cast<TX*>(smem_raw);                                        // [RT_TOK][H]
     float* probs = reinterpret_cast<float*>(smem_raw + sizeof(TX) * RT_TOK * H);     // [RT_TOK][2 E]
@@ -90,7 +91,8 @@ __global__ void __launch_bounds__(256) router_topk_kernel(
         for (int t = 0; t < RT_TOK; ++t) {
             if (t < nt) {
                 const float s = warp_sum(acc[t]);
-                if (lane == 0) logits[static_cast<size_t>(t0 + t) * E1 + e] = s;
+                // a router with a bias of its own: part of the logit, for the selection and the weights alike
+                if (lane == 0) logits[static_cast<size_t>(t0 + t) * E1 + e] = s + (logit_bias != nullptr && e < E ? logit_bias[e] : 0.f);
             }
         }
     }
@@ -114,7 +116,7 @@ extern "C" int locus_router_topk(const void* h, int x_dt, const void* wr, int w_
                                  int wg_dt, float* logits, int* counters, int* ids, float* wts,
                                  float* gamma, int T, int H, int E, int k, int renorm, float scale,
                                  int score_fn, const float* sel_bias, int n_group, int n_group_used,
-                                 cudaStream_t stream) {
+                                 const float* logit_bias, cudaStream_t stream) {
     if (T <= 0) return 0;
     const RouteOpts o{k, renorm, score_fn, n_group, n_group_used, scale, sel_bias};
     if (!route_opts_ok(o, E)) return LOCUS_ERR_UNSUPPORTED;
@@ -131,7 +133,7 @@ extern "C" int locus_router_topk(const void* h, int x_dt, const void* wr, int w_
                                  cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);       \
         router_topk_kernel<TX, TW><<<grid, 256, smem, stream>>>(                                 \
             static_cast<const TX*>(h), static_cast<const TW*>(wr), wg, wg_dt, logits, counters,  \
-            ids, wts, gamma, T, H, E, o);                                                        \
+            ids, wts, gamma, T, H, E, o, logit_bias);                                            \
     } while (0)
     if (x_dt == LOCUS_DT_F32 && w_dt == LOCUS_DT_F32) ROUTER_LAUNCH(float, float);
     else if (x_dt == LOCUS_DT_BF16 && w_dt == LOCUS_DT_BF16) ROUTER_LAUNCH(bf16, bf16);

@@ -430,6 +430,10 @@ def expert_tile(n_pairs: int, n_experts: int) -> int:
     return 128
 
 
+# activations of a product's epilogue, by their code in the kernels' flags
+ACTIVATIONS = {None: 0, "relu2": 1}
+
+
 def tc_error() -> int:
     """Error word of the tensor-core module (0 = fine); reading it synchronises the device.
     Non-zero: a bounded wait inside a kernel ran out (1 producer, 2 MMA, 3 epilogue)."""
@@ -440,10 +444,11 @@ def linear(x: torch.Tensor, w: torch.Tensor, out: torch.Tensor, *, w2: Optional[
            bias: Optional[torch.Tensor] = None, accumulate: bool = False,
            row_scale: Optional[torch.Tensor] = None, scale_rows: Optional[torch.Tensor] = None,
            x_rows: Optional[torch.Tensor] = None, x_row_div: int = 1, layout: Optional[ExpertLayout] = None,
-           n_rows: Optional[int] = None, lists_ready: bool = False, second_tiles: bool = False) -> None:
+           n_rows: Optional[int] = None, lists_ready: bool = False, second_tiles: bool = False,
+           act: Optional[str] = None) -> None:
     """out = x . w^T with float32 accumulation on CUDA cores (see csrc/gemm_simt.cu).
 
-    ``w2``: out = silu(x . w^T) * (x . w2^T).  ``bias`` [N] is added, ``row_scale`` [M]
+    ``w2``: out = silu(x . w^T) * (x . w2^T).  ``act`` = "relu2": out = max(x . w^T + bias, 0)^2 (not with ``w2``).  ``bias`` [N] is added, ``row_scale`` [M]
     multiplies the row (``scale_rows``: row m uses row_scale[scale_rows[m]]), ``accumulate`` adds the result into the float32 ``out``.
     ``x_rows``: logical row m reads x[x_rows[m] // x_row_div].  ``layout``: grouped product,
     ``w`` is [E, N, K] and logical rows are the expert-sorted pairs of the layout.
@@ -468,6 +473,8 @@ def linear(x: torch.Tensor, w: torch.Tensor, out: torch.Tensor, *, w2: Optional[
         _need(w2.shape == w.shape and w2.dtype == w.dtype and w2.is_contiguous(), "linear: w2 must match w")
     if accumulate:
         _need(out.dtype == torch.float32, "linear: accumulate needs a float32 out")
+    _need(act in ACTIVATIONS and not (act and w2 is not None), f"linear: activation {act!r} (known: relu2; not with w2)")
+    flags = I((1 if accumulate else 0) | (ACTIVATIONS[act] << 1))
     if bias is not None:
         _need(bias.numel() == N and bias.is_contiguous(), "linear: bias size")
     if row_scale is not None:
@@ -493,7 +500,7 @@ def linear(x: torch.Tensor, w: torch.Tensor, out: torch.Tensor, *, w2: Optional[
             max_tiles = stride = 0
         code = _lib("gemm_skinny").locus_gemm_skinny(
             _p(x), _p(w), _p(w2), _p(bias), I(dtype_code(bias.dtype) if bias is not None else 0), _p(out),
-            I(dtype_code(out.dtype)), I(1 if accumulate else 0), _p(row_scale), _p(scale_rows), _p(x_rows),
+            I(dtype_code(out.dtype)), flags, _p(row_scale), _p(scale_rows), _p(x_rows),
             I(x_row_div), I(M), I(N), I(K), LL(x.stride(0)), LL(out.stride(0)), I(tile), _p(te), _p(t0), _p(tr),
             _p(nt), I(max_tiles), LL(stride), I(1 if (lists_ready and layout is not None) else 0), _stream()
         )
@@ -511,7 +518,7 @@ def linear(x: torch.Tensor, w: torch.Tensor, out: torch.Tensor, *, w2: Optional[
         code = _lib("gemv").locus_gemv(
             _p(x), I(dtype_code(x.dtype)), _p(w), _p(w2), I(dtype_code(w.dtype)), _p(bias),
             I(dtype_code(bias.dtype) if bias is not None else 0), _p(out), I(dtype_code(out.dtype)),
-            I(1 if accumulate else 0), _p(row_scale), _p(scale_rows), _p(x_rows), I(x_row_div), I(M), I(N), I(K),
+            flags, _p(row_scale), _p(scale_rows), _p(x_rows), I(x_row_div), I(M), I(N), I(K),
             LL(x.stride(0)), LL(out.stride(0)), _p(te), _p(t0), _p(tr), _p(nt), I(max_tiles), LL(stride), _stream()
         )
         _check(code, "linear", f"(few rows; M={M}, N={N}, K={K}, x {x.dtype}, w {w.dtype})")
@@ -529,6 +536,9 @@ def linear(x: torch.Tensor, w: torch.Tensor, out: torch.Tensor, *, w2: Optional[
         else:
             _need(w.dim() == 2, "linear: w must be [N, K]")
             TN, splits = tc_plan(M, N, K, w2 is not None)
+            if act and splits > 1:
+                # the activation belongs behind the whole sum: such a product is not cut along K
+                TN, splits = tc_plan(M, N, K, True)[0], 1
             if splits > 1:
                 scratch = _split_scratch(x.device)
             te = t0 = tr = nt = None
@@ -536,7 +546,7 @@ def linear(x: torch.Tensor, w: torch.Tensor, out: torch.Tensor, *, w2: Optional[
         code = _lib("gemm_tc").locus_gemm_tc(
             _p(x), LL(M), LL(x.stride(0)), _p(w), _p(w2), LL(w.numel() // K), _p(bias),
             I(dtype_code(bias.dtype) if bias is not None else 0), _p(out), I(dtype_code(out.dtype)),
-            I(1 if accumulate else 0), _p(row_scale), _p(scale_rows), I(M), I(N), I(K), LL(out.stride(0)), I(TN),
+            flags, _p(row_scale), _p(scale_rows), I(M), I(N), I(K), LL(out.stride(0)), I(TN),
             _p(te), _p(t0), _p(tr), _p(nt), I(max_tiles), _p(scratch if splits > 1 else None), I(splits), _stream()
         )
         if splits > 1 and code == 0:
@@ -556,7 +566,7 @@ def linear(x: torch.Tensor, w: torch.Tensor, out: torch.Tensor, *, w2: Optional[
     code = _lib("gemm_simt").locus_gemm_simt(
         _p(x), I(dtype_code(x.dtype)), _p(w), _p(w2), I(dtype_code(w.dtype)), _p(bias),
         I(dtype_code(bias.dtype) if bias is not None else 0), _p(out), I(dtype_code(out.dtype)),
-        I(1 if accumulate else 0), _p(row_scale), _p(scale_rows), _p(x_rows), I(x_row_div), I(M), I(N), I(K),
+        flags, _p(row_scale), _p(scale_rows), _p(x_rows), I(x_row_div), I(M), I(N), I(K),
         LL(x.stride(0)), LL(out.stride(0)), _p(te), _p(t0), _p(tr), _p(nt), I(max_tiles), LL(stride),
         _stream()
     )
@@ -913,11 +923,13 @@ class RouterScratch:
 def router_topk(h: torch.Tensor, w_router: torch.Tensor, w_gate: Optional[torch.Tensor],
                 ids: torch.Tensor, wts: torch.Tensor, gamma: Optional[torch.Tensor], *, top_k: int,
                 renorm: bool, scale: float = 1.0, scratch: Optional[RouterScratch] = None, score_fn: str = "softmax",
-                sel_bias: Optional[torch.Tensor] = None, n_group: int = 1, n_group_used: int = 1) -> None:
+                sel_bias: Optional[torch.Tensor] = None, n_group: int = 1, n_group_used: int = 1,
+                logit_bias: Optional[torch.Tensor] = None) -> None:
     """Router: scores of all experts (``score_fn``: softmax over them, or a sigmoid of each logit), top-k by
     repeated arg-max, weights; and gamma = sigmoid(w_gate . h) when the shared expert is gated.  All in float32.
     ``sel_bias`` [E] is added to the scores for the selection only; with ``n_group`` > 1 only the
-    ``n_group_used`` groups of experts with the best two-score sums are eligible.
+    ``n_group_used`` groups of experts with the best two-score sums are eligible.  ``logit_bias`` [E] float32 is
+    part of the logits (a router with a bias of its own): it enters the scores, the selection and the weights.
     ``scratch`` must hold T tokens of E (+1 with a gate) logits (made on the fly when None)."""
     _cuda_c(h, "h")
     _cuda_c(w_router, "w_router")
@@ -938,13 +950,22 @@ def router_topk(h: torch.Tensor, w_router: torch.Tensor, w_gate: Optional[torch.
         _p(h), I(dtype_code(h.dtype)), _p(w_router), I(dtype_code(w_router.dtype)), _p(w_gate),
         I(dtype_code(w_gate.dtype) if w_gate is not None else 0), _p(scratch.logits), _p(scratch.counters),
         _p(ids), _p(wts), _p(gamma), I(T), I(H), I(E), I(top_k), I(1 if renorm else 0), F(scale),
-        *_route_rule(score_fn, sel_bias, n_group, n_group_used, E, "router_topk"), _stream()
+        *_route_rule(score_fn, sel_bias, n_group, n_group_used, E, "router_topk"), _p(_logit_bias(logit_bias, E)),
+        _stream()
     )
     _check(code, "router_topk", f"(H={H}, E={E}, k={top_k})")
 
 
-def router_logits(h: torch.Tensor, w_all: torch.Tensor, logits: torch.Tensor) -> None:
-    """logits[t, e] = w_all[e] . h[t] in float32 with the weight-streaming tensor-core kernel,
+def _logit_bias(b: Optional[torch.Tensor], n: int) -> Optional[torch.Tensor]:
+    if b is not None:
+        _need(b.is_cuda and b.dtype == torch.float32 and b.is_contiguous() and b.numel() >= n,
+              "router: the logit bias must be float32, one number per logit row")
+    return b
+
+
+def router_logits(h: torch.Tensor, w_all: torch.Tensor, logits: torch.Tensor,
+                  bias: Optional[torch.Tensor] = None) -> None:
+    """logits[t, e] = w_all[e] . h[t] (+ ``bias[e]``, float32) in float32 with the weight-streaming tensor-core kernel,
     for ANY number of tokens (tiles of up to 16): one kernel, and one order of the sum, for
     every batch shape.  bfloat16 ``h`` [T, H] and ``w_all`` [E (+1), H]; ``logits`` [T, >= E (+1)]."""
     _cuda_c(h, "h")
@@ -958,7 +979,7 @@ def router_logits(h: torch.Tensor, w_all: torch.Tensor, logits: torch.Tensor) ->
     # 8,192 tokens: 60 against 34), and the order of a sum does not depend on the tile
     tile = 8 if T <= 8 else 16
     code = _lib("gemm_skinny").locus_gemm_skinny(
-        _p(h), _p(w_all), None, None, I(0), _p(logits), I(0), I(0), None, None, None, I(1), I(T), I(n), I(H),
+        _p(h), _p(w_all), None, _p(_logit_bias(bias, n)), I(0), _p(logits), I(0), I(0), None, None, None, I(1), I(T), I(n), I(H),
         LL(h.stride(0)), LL(logits.stride(0)), I(tile), None, None, None, None, I(0), LL(0), I(0), _stream()
     )
     _check(code, "router_logits", f"(T={T}, H={H}, rows {n})")
@@ -1050,8 +1071,8 @@ def route_fused_small(h: torch.Tensor, w_all: torch.Tensor, logits: torch.Tensor
                       ids: torch.Tensor, wts: torch.Tensor, gamma: Optional[torch.Tensor], layout: ExpertLayout,
                       counter: torch.Tensor, *, n_tokens: int, top_k: int, renorm: bool, scale: float = 1.0,
                       tile_m: Optional[int] = None, score_fn: str = "softmax", sel_bias: Optional[torch.Tensor] = None,
-                      n_group: int = 1, n_group_used: int = 1) -> None:
-    """:func:`router_logits` followed by :func:`route_small` in ONE launch, for batches that ``route_small_takes``:
+                      n_group: int = 1, n_group_used: int = 1, logit_bias: Optional[torch.Tensor] = None) -> None:
+    """:func:`router_logits` (with ``logit_bias`` as its bias) followed by :func:`route_small` in ONE launch, for batches that ``route_small_takes``:
     the same logits (the same kernel computes them), picks, weights and layout.  ``counter``: one int32 that is
     zero before the call and zero after it."""
     _need(route_small_takes(n_tokens, top_k, n_experts), "route_fused_small: batch too large")
@@ -1079,7 +1100,7 @@ def route_fused_small(h: torch.Tensor, w_all: torch.Tensor, logits: torch.Tensor
         LL(h.stride(0)), I(n_experts), I(top_k), I(1 if has_gate else 0), I(1 if renorm else 0), F(scale),
         *_route_rule(score_fn, sel_bias, n_group, n_group_used, n_experts, "route_fused_small"), I(layout.tile_m),
         _p(layout.counts), _p(layout.offsets), _p(layout.sorted_pair), _p(layout.pair_pos), _p(layout.tile_expert),
-        _p(layout.tile_row0), _p(layout.tile_rows), _p(layout.n_tiles), _stream()
+        _p(layout.tile_row0), _p(layout.tile_rows), _p(layout.n_tiles), _p(_logit_bias(logit_bias, n)), _stream()
     )
     _check(code, "route_fused_small", f"(T={T}, E={n_experts}, k={top_k})")
 
@@ -1108,6 +1129,205 @@ def gather_rows(src: torch.Tensor, idx: torch.Tensor, div: int, out: torch.Tenso
     code = _lib("elementwise").locus_gather_rows(_p(src), I(dtype_code(src.dtype)), _p(idx), I(div), _p(out),
                                                  I(n), I(src.shape[-1]), _stream())
     _check(code, "gather_rows")
+
+
+# ---------------------------------------------------------------------------
+# sublayers that read the residual stream themselves and are normed on the way out
+D = ctypes.c_double
+
+
+def cast_rows(x: torch.Tensor, out: torch.Tensor) -> None:
+    """out[i, :] = x[i, :] (float32 rows) in ``out``'s element type."""
+    _cuda_c(x, "x")
+    _cuda_c(out, "out")
+    _need(x.dtype == torch.float32 and x.shape == out.shape, "cast_rows: float32 rows into rows of the same shape")
+    code = _lib("elementwise").locus_cast_rows(_p(x), _p(out), I(dtype_code(out.dtype)), LL(x.numel()), _stream())
+    _check(code, "cast_rows")
+
+
+def rmsnorm_add(y: torch.Tensor, w: torch.Tensor, eps: float, x: torch.Tensor) -> None:
+    """x[i] += y[i] * rsqrt(mean(y[i]^2) + eps) * w: the norm of a sublayer's output, added to the float32
+    residual stream (statistics in float32)."""
+    _cuda_c(y, "y")
+    _cuda_c(w, "w")
+    _cuda_c(x, "x")
+    _need(y.dtype == torch.float32 and x.dtype == torch.float32 and y.shape == x.shape and w.numel() == y.shape[-1],
+          "rmsnorm_add: float32 y and x of one shape, w of their width")
+    code = _lib("elementwise").locus_rmsnorm_add(_p(y), _p(w), I(dtype_code(w.dtype)), F(eps), _p(x), I(y.shape[0]),
+                                                 I(y.shape[-1]), _stream())
+    _check(code, "rmsnorm_add")
+
+
+# ---------------------------------------------------------------------------
+# latent attention (csrc/latent_attention.cu)
+LATENT_QUERY_TILE = 16   # queries per work item of latent_attn
+LATENT_MAX_RANK = 512
+
+
+def _freq(freq: Optional[torch.Tensor], rot_pairs: int, what: str) -> None:
+    if rot_pairs > 0:
+        _need(freq is not None and freq.is_cuda and freq.dtype == torch.float64 and freq.numel() >= rot_pairs,
+              f"{what}: the frequencies must be float64 [rot_pairs] on the device")
+
+
+def latent_prep(dqkv: torch.Tensor, positions: torch.Tensor, freq: Optional[torch.Tensor], magnitude: float,
+                w_q: torch.Tensor, w_kv: torch.Tensor, eps: float, cq_out: torch.Tensor, pool: torch.Tensor,
+                slots: torch.Tensor, *, q_rank: int, kv_rank: int, rot_dim: int, rot_pairs: int,
+                write: bool = True) -> None:
+    """From the stacked down-projections ``dqkv`` [T, q_rank + kv_rank + rot_dim] (float32): the normed query
+    latent into ``cq_out`` [T, q_rank]; the normed key/value latent and the rotated shared key part into the
+    token's cache row (``pool`` [n_pages, 1, 1, page_tokens, kv_rank + rot_dim], ``slots[t]`` = page *
+    page_tokens + offset).  Interleaved pairs (2i, 2i + 1), i < ``rot_pairs``, are turned by
+    position * freq[i]; cosine and sine are multiplied by ``magnitude``."""
+    _cuda_c(dqkv, "dqkv")
+    _cuda_c(cq_out, "cq_out")
+    _cuda_c(pool, "pool")
+    _i32(positions, "positions")
+    _i32(slots, "slots")
+    T = dqkv.shape[0]
+    _need(dqkv.dtype == torch.float32 and dqkv.shape[1] == q_rank + kv_rank + rot_dim, "latent_prep: dqkv float32 of the stacked width")
+    _need(cq_out.dtype == pool.dtype and cq_out.shape[0] >= T and cq_out.shape[1] == q_rank, "latent_prep: cq_out")
+    _need(pool.shape[-1] == kv_rank + rot_dim and pool.shape[1] == 1 and pool.shape[2] == 1, "latent_prep: pool layout")
+    _need(w_q.dtype == w_kv.dtype and w_q.numel() == q_rank and w_kv.numel() == kv_rank and w_q.is_cuda and w_kv.is_cuda,
+          "latent_prep: norm weights")
+    _need(positions.numel() >= T and slots.numel() >= T, "latent_prep: T mismatch")
+    _freq(freq, rot_pairs, "latent_prep")
+    code = _lib("latent_attention").locus_latent_prep(
+        _p(dqkv), _p(positions), _p(freq), F(magnitude), _p(w_q), _p(w_kv), I(dtype_code(w_q.dtype)), F(eps),
+        _p(cq_out), _p(pool), I(dtype_code(pool.dtype)), _p(slots), I(T), I(q_rank), I(kv_rank), I(rot_dim),
+        I(rot_pairs), I(1 if write else 0), _stream())
+    _check(code, "latent_prep")
+
+
+def latent_q_split(q: torch.Tensor, positions: torch.Tensor, freq: Optional[torch.Tensor], magnitude: float,
+                   q_nope_hm: torch.Tensor, q_rot: torch.Tensor, *, n_heads: int, nope_dim: int, rot_dim: int,
+                   rot_pairs: int) -> None:
+    """``q`` [T, H * (nope_dim + rot_dim)], head by head [unrotated | rotated]: the unrotated parts go to
+    ``q_nope_hm`` [H * T, nope_dim] (head-major: row h * T + t), the rotated parts, turned by the token's
+    position, to ``q_rot`` [T, H * rot_dim]."""
+    _cuda_c(q, "q")
+    _cuda_c(q_nope_hm, "q_nope_hm")
+    _cuda_c(q_rot, "q_rot")
+    _i32(positions, "positions")
+    T = q.shape[0]
+    _need(q.shape[1] == n_heads * (nope_dim + rot_dim) and q.dtype == q_nope_hm.dtype == q_rot.dtype, "latent_q_split: q")
+    _need(q_nope_hm.shape[0] >= n_heads * T and q_nope_hm.shape[1] == nope_dim, "latent_q_split: q_nope_hm")
+    _need(q_rot.shape[0] >= T and q_rot.shape[1] == n_heads * rot_dim, "latent_q_split: q_rot")
+    _freq(freq, rot_pairs, "latent_q_split")
+    code = _lib("latent_attention").locus_latent_q_split(
+        _p(q), I(dtype_code(q.dtype)), _p(positions), _p(freq), F(magnitude), _p(q_nope_hm), _p(q_rot), I(T),
+        I(n_heads), I(nope_dim), I(rot_dim), I(rot_pairs), _stream())
+    _check(code, "latent_q_split")
+
+
+def latent_attn(q_abs_hm: torch.Tensor, q_rot: torch.Tensor, pool: torch.Tensor, sink: Optional[torch.Tensor],
+                out_hm: torch.Tensor, *, seg_q0: torch.Tensor, seg_qn: torch.Tensor, seg_ctx: torch.Tensor,
+                block_table: torch.Tensor, items: torch.Tensor, n_items: int, n_tokens: int, n_heads: int,
+                kv_rank: int, rot_dim: int, page_tokens: int, window: int, scale: float) -> None:
+    """Attention over latent cache rows [latent (kv_rank) | rotated key part (rot_dim)] that all heads share:
+    score = (q_abs . latent + q_rot . key part) * scale over the keys a query sees (``window`` > 0: the last
+    ``window`` positions, itself included), softmax whose denominator also holds exp(sink[h]) when ``sink`` is
+    given, output = sum of p * latent.  ``q_abs_hm`` and ``out_hm`` are head-major [H * T, kv_rank]; ``items``
+    [n_items, 2] = (segment, first query of a tile of ``LATENT_QUERY_TILE`` queries within it)."""
+    _cuda_c(q_abs_hm, "q_abs_hm")
+    _cuda_c(q_rot, "q_rot")
+    _cuda_c(pool, "pool")
+    _cuda_c(out_hm, "out_hm")
+    _i32(block_table, "block_table")
+    _i32(items, "items")
+    T = n_tokens
+    _need(q_abs_hm.dtype == q_rot.dtype == pool.dtype == out_hm.dtype, "latent_attn: one element type")
+    _need(q_abs_hm.shape[0] >= n_heads * T and q_abs_hm.shape[1] == kv_rank and out_hm.shape[0] >= n_heads * T
+          and out_hm.shape[1] == kv_rank and q_rot.shape[0] >= T and q_rot.shape[1] == n_heads * rot_dim,
+          "latent_attn: shapes")
+    _need(pool.shape[-1] == kv_rank + rot_dim and pool.shape[-2] == page_tokens, "latent_attn: pool layout")
+    if sink is not None:
+        _need(sink.is_cuda and sink.dtype == torch.float32 and sink.numel() == n_heads and sink.is_contiguous(),
+              "latent_attn: sink must be float32 [H]")
+    code = _lib("latent_attention").locus_latent_attn(
+        _p(q_abs_hm), _p(q_rot), I(dtype_code(pool.dtype)), _p(pool), _p(sink), _p(out_hm), _p(seg_q0), _p(seg_qn),
+        _p(seg_ctx), _p(block_table), I(block_table.shape[1]), _p(items), I(n_items), I(T), I(n_heads), I(kv_rank),
+        I(rot_dim), I(page_tokens), I(window), F(scale), _stream())
+    _check(code, "latent_attn", f"(heads {n_heads}, latent {kv_rank} + {rot_dim})")
+
+
+def heads_to_rows(src_hm: torch.Tensor, out: torch.Tensor, *, n_tokens: int, n_heads: int) -> None:
+    """``src_hm`` [H * T, d] head-major -> ``out`` [T, H * d]."""
+    _cuda_c(src_hm, "src_hm")
+    _cuda_c(out, "out")
+    d = src_hm.shape[1]
+    _need(src_hm.dtype == out.dtype and src_hm.shape[0] >= n_heads * n_tokens and out.shape[0] >= n_tokens
+          and out.shape[1] == n_heads * d, "heads_to_rows: shapes")
+    code = _lib("latent_attention").locus_heads_to_rows(_p(src_hm), I(dtype_code(out.dtype)), _p(out), I(n_tokens),
+                                                        I(n_heads), I(d), _stream())
+    _check(code, "heads_to_rows")
+
+
+class HeadLayout:
+    """The tile lists of a grouped product whose groups are the heads of a head-major tensor [H * T, ...]: head
+    h owns the rows h * T .. (h + 1) * T.  It stands where :func:`linear` takes an :class:`ExpertLayout`; the lists
+    themselves are device views that the step's plan wrote (parts.latent_attention.HeadTiles)."""
+
+    def __init__(self, n_heads: int, tile_m: int, offsets, tile_expert, tile_row0, tile_rows, n_tiles,
+                 max_tiles: int) -> None:
+        self.n_experts, self.tile_m, self.tile2_m = n_heads, tile_m, 0
+        self.offsets, self.tile_expert, self.tile_row0, self.tile_rows = offsets, tile_expert, tile_row0, tile_rows
+        self.n_tiles, self.max_tiles = n_tiles, max_tiles
+
+    def tiles_for(self, n_pairs: int, tile_m: Optional[int] = None) -> int:
+        return self.max_tiles
+
+
+def head_tile(n_tokens: int, dtype: torch.dtype, widths_ok: bool) -> int:
+    """Row tile of the per-head products of ``n_tokens`` rows a head, by the kernel that :func:`linear` picks for
+    it: 8 rows on the row-streaming kernels, 128 on the tcgen05 kernel, 64 on the CUDA cores."""
+    if widths_ok and n_tokens <= FEW_ROWS:
+        return FEW_ROWS
+    if widths_ok and USE_TENSOR_CORES and dtype == torch.bfloat16:
+        return 128
+    return 64
+
+
+# ---------------------------------------------------------------------------
+# retention (csrc/retention.cu)
+RETENTION_MAX_DIM = 256
+
+
+def retention_scan(qkvg: torch.Tensor, state: torch.Tensor, state_slots: torch.Tensor, seg_q0: torch.Tensor,
+                   seg_qn: torch.Tensor, n_seg: int, decay: torch.Tensor, k_scale: float, o_raw: torch.Tensor, *,
+                   n_heads: int, dim: int, v_dim: int) -> None:
+    """The recurrence S = decay[h] * S + (k * k_scale) v^T, o = S^T q over every segment's new tokens in order,
+    from and into ``state`` [n_slots, H, dim, v_dim] (float32) of the segment's slot.  ``qkvg`` [T, >= 2 H dim +
+    2 H v_dim] float32 with the columns [q | k | v | gate]; ``o_raw`` [T, H * v_dim] float32."""
+    _cuda_c(qkvg, "qkvg")
+    _cuda_c(state, "state")
+    _cuda_c(o_raw, "o_raw")
+    _i32(state_slots, "state_slots")
+    _need(qkvg.dtype == state.dtype == o_raw.dtype == decay.dtype == torch.float32, "retention_scan: float32 throughout")
+    _need(tuple(state.shape[1:]) == (n_heads, dim, v_dim) and decay.numel() == n_heads and decay.is_cuda,
+          "retention_scan: state [slots, H, dim, v_dim], decay [H]")
+    _need(o_raw.shape[1] == n_heads * v_dim and o_raw.shape[0] >= qkvg.shape[0], "retention_scan: o_raw")
+    code = _lib("retention").locus_retention_scan(
+        _p(qkvg), I(qkvg.stride(0)), _p(state), _p(state_slots), _p(seg_q0), _p(seg_qn), I(n_seg), _p(decay),
+        F(k_scale), _p(o_raw), I(n_heads), I(dim), I(v_dim), _stream())
+    _check(code, "retention_scan", f"(heads {n_heads}, dim {dim}, v_dim {v_dim})")
+
+
+def retention_gate_norm(o_raw: torch.Tensor, qkvg: torch.Tensor, gate_offset: int, eps: float, out: torch.Tensor, *,
+                        n_heads: int, v_dim: int) -> None:
+    """out[t, h, :] = o_raw[t, h, :] / rms(o_raw[t, h, :]) * silu(gate[t, h, :]), the gate being the columns of
+    ``qkvg`` from ``gate_offset`` on."""
+    _cuda_c(o_raw, "o_raw")
+    _cuda_c(qkvg, "qkvg")
+    _cuda_c(out, "out")
+    T = out.shape[0]
+    _need(o_raw.dtype == qkvg.dtype == torch.float32 and o_raw.shape[0] >= T and qkvg.shape[0] >= T
+          and o_raw.shape[1] == out.shape[1] == n_heads * v_dim and qkvg.shape[1] >= gate_offset + n_heads * v_dim,
+          "retention_gate_norm: shapes")
+    code = _lib("retention").locus_retention_gate_norm(_p(o_raw), _p(qkvg), I(qkvg.stride(0)), I(gate_offset), F(eps),
+                                                       _p(out), I(dtype_code(out.dtype)), I(T), I(n_heads), I(v_dim),
+                                                       _stream())
+    _check(code, "retention_gate_norm")
 
 
 def apply_penalties(logits: torch.Tensor, history: torch.Tensor, repeat: torch.Tensor,

@@ -119,6 +119,8 @@ class Attention(Mixer):
         qkv = rt.rows("attention.qkv", self.q_dim + 2 * self.kv_dim, rt.dtype, T)
         K.linear(h, self.params["wqkv"], qkv, bias=self.params.get("bqkv"))
         table = self.position.rotary_table()
+        if table is not None and table.magnitude != 1.0:
+            raise ValueError("attention: the fused rotation takes no factor on cosine and sine")
         if table is None:
             # an encoding without a rotary table transforms q and k in place itself
             self.position.apply(qkv[:, : self.q_dim], qkv[:, self.q_dim : self.q_dim + self.kv_dim],

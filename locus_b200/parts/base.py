@@ -174,6 +174,11 @@ class Norm(Part):
         has to show in ``out``."""
         raise NotImplementedError
 
+    def forward_add(self, y: torch.Tensor, x: torch.Tensor) -> None:
+        """x += norm(y) for float32 rows y of a sublayer's output (arrangements that norm what a sublayer
+        gives instead of what it reads)."""
+        raise NotImplementedError
+
 
 class PositionEncoding(Part):
     """How a mixer encodes positions.  A rotary encoding exposes its table so that the
@@ -192,6 +197,8 @@ class RotaryTable:
     inv_freq: torch.Tensor  # float32 [rot_dim / 2] on the device
     rot_dim: int
     interleaved: bool
+    magnitude: float = 1.0                      # factor on cosine and sine
+    freq64: Optional[torch.Tensor] = None       # the same frequencies in float64, for angles formed in float64
 
 
 class StepPlan:
@@ -226,6 +233,10 @@ class Mixer(Part):
         """Host-planned work lists this mixer wants for every step (see :class:`StepPlan`)."""
         return []
 
+    # A part with ``can_overwrite`` takes ``accumulate=False`` in ``forward``: it then WRITES its output into
+    # ``residual`` (float32 rows whose old contents do not matter) instead of adding to it.
+    can_overwrite = False
+
     def forward(self, h: torch.Tensor, batch: "StepBatch", cache: "LayerCache",
                 residual: torch.Tensor, rt: "Runtime") -> None:
         """Add the mixer's output for the ``batch.T`` rows of ``h`` into ``residual`` (float32)."""
@@ -233,6 +244,8 @@ class Mixer(Part):
 
 
 class FeedForward(Part):
+    can_overwrite = False   # as for Mixer
+
     def forward(self, h: torch.Tensor, batch: "StepBatch", residual: torch.Tensor, rt: "Runtime") -> None:
         """Add the feed-forward output of ``h`` into ``residual`` (float32)."""
         raise NotImplementedError

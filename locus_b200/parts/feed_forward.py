@@ -17,44 +17,64 @@ tokens, and sums each token's pairs in slot order without atomics (the reference
 """
 from __future__ import annotations
 
+from typing import Optional
+
 import torch
 
 from .. import kernels as K
 from .base import FeedForward, PendingAdd, TensorSource, register_feed_forward
 
 
+ACTIVATIONS = ("swiglu", "relu2")
+# tensor names below a feed-forward's prefix, by role; an architecture with other names passes its own
+DENSE_NAMES = {"gate": "gate_proj.weight", "up": "up_proj.weight", "down": "down_proj.weight"}
+
+
 class DenseMlp(FeedForward):
-    def __init__(self, prefix: str, *, hidden: int, intermediate: int) -> None:
+    """``activation`` "swiglu": down(silu(gate h) * (up h)); "relu2": down(max(up h, 0)^2), no gate matrix."""
+
+    can_overwrite = True
+
+    def __init__(self, prefix: str, *, hidden: int, intermediate: int, activation: str = "swiglu",
+                 names: Optional[dict] = None) -> None:
         super().__init__(prefix)
-        self.hidden, self.inter = int(hidden), int(intermediate)
+        if activation not in ACTIVATIONS:
+            raise ValueError(f"dense_mlp: activation {activation!r} (known: {', '.join(ACTIVATIONS)})")
+        self.hidden, self.inter, self.activation = int(hidden), int(intermediate), activation
+        self.names = {**DENSE_NAMES, **(names or {})}
 
     def param_shapes(self):
-        return {"w_gate": (self.inter, self.hidden), "w_up": (self.inter, self.hidden),
-                "w_down": (self.hidden, self.inter)}
+        s = {"w_up": (self.inter, self.hidden), "w_down": (self.hidden, self.inter)}
+        if self.activation == "swiglu":
+            s["w_gate"] = (self.inter, self.hidden)
+        return s
 
     def sources(self):
-        p = self.prefix
-        return [
-            TensorSource(f"{p}.gate_proj.weight", (self.inter, self.hidden), "w_gate"),
-            TensorSource(f"{p}.up_proj.weight", (self.inter, self.hidden), "w_up"),
-            TensorSource(f"{p}.down_proj.weight", (self.hidden, self.inter), "w_down"),
-        ]
+        p, n = self.prefix, self.names
+        out = [TensorSource(f"{p}.{n['up']}", (self.inter, self.hidden), "w_up"),
+               TensorSource(f"{p}.{n['down']}", (self.hidden, self.inter), "w_down")]
+        if self.activation == "swiglu":
+            out.insert(0, TensorSource(f"{p}.{n['gate']}", (self.inter, self.hidden), "w_gate"))
+        return out
 
     def kernel_modules(self, dtype):
         return ["gemm_simt", "gemv"] + (["gemm_skinny", "gemm_tc"] if dtype == torch.bfloat16 else [])
 
-    def forward(self, h, batch, residual, rt, row_scale=None) -> None:
-        self.forward_down(self.forward_up(h, rt), residual, rt, row_scale)
+    def forward(self, h, batch, residual, rt, row_scale=None, accumulate=True) -> None:
+        self.forward_down(self.forward_up(h, rt), residual, rt, row_scale, accumulate)
 
     # The two products on their own, for a caller that has something to do between them (the shared expert of a
     # routed feed-forward starts before the router has made the scale of its second product).
     def forward_up(self, h, rt) -> torch.Tensor:
         act = rt.rows(f"dense_mlp.act{self.inter}", self.inter, rt.dtype, h.shape[0])
-        K.linear(h, self.params["w_gate"], act, w2=self.params["w_up"])
+        if self.activation == "swiglu":
+            K.linear(h, self.params["w_gate"], act, w2=self.params["w_up"])
+        else:
+            K.linear(h, self.params["w_up"], act, act="relu2")
         return act
 
-    def forward_down(self, act, residual, rt, row_scale=None) -> None:
-        K.linear(act, self.params["w_down"], residual, accumulate=True, row_scale=row_scale)
+    def forward_down(self, act, residual, rt, row_scale=None, accumulate=True) -> None:
+        K.linear(act, self.params["w_down"], residual, accumulate=accumulate, row_scale=row_scale)
 
 
 # Up to this many tokens in a step the shared expert's first product starts beside the router instead of behind it
@@ -65,14 +85,28 @@ SHARED_OVERLAP_FROM = 1024   # steps of at least this many tokens ...
 SHARED_OVERLAP_ROWS = 192    # ... and at most this many rows per routed expert run the shared expert on the side stream
 
 
+# tensor names below a routed feed-forward's prefix ({e}: the expert's number)
+MOE_NAMES = {"router": "gate.weight", "router_bias": "gate.bias", "selection_bias": "gate.selection_bias",
+             "expert_gate": "experts.{e}.gate_proj.weight", "expert_up": "experts.{e}.up_proj.weight",
+             "expert_down": "experts.{e}.down_proj.weight", "shared": "shared_expert",
+             "shared_gate": "shared_expert_gate.weight"}
+
+
 class SparseMoe(FeedForward):
-    """Softmax top-k routed SwiGLU experts plus an optional (gated) shared SwiGLU expert."""
+    """Softmax top-k routed experts plus an optional (gated) shared expert; the experts are SwiGLU layers or, with
+    ``activation`` "relu2", down(max(up h, 0)^2)."""
+
+    can_overwrite = True
 
     def __init__(self, prefix: str, *, hidden: int, n_experts: int, top_k: int, norm_topk: bool,
                  expert_intermediate: int, shared_intermediate: int = 0, shared_gate: bool = True,
                  weight_scale: float = 1.0, score_fn: str = "softmax", selection_bias: bool = False,
-                 n_group: int = 1, n_group_used: int = 1) -> None:
-        """``score_fn``: "softmax" over all experts or "sigmoid" of each router logit; ``selection_bias``:
+                 n_group: int = 1, n_group_used: int = 1, activation: str = "swiglu", router_bias: bool = False,
+                 names: Optional[dict] = None, shared_names: Optional[dict] = None) -> None:
+        """``router_bias``: the router has a bias [n_experts] that is part of its logits (selection and weights
+        alike; with softmax scores and ``norm_topk`` the weights are then the softmax over the picked logits).
+        ``names`` / ``shared_names``: tensor names where they differ from ``MOE_NAMES`` / ``DENSE_NAMES``.
+        ``score_fn``: "softmax" over all experts or "sigmoid" of each router logit; ``selection_bias``:
         a float32 tensor ``<prefix>.gate.selection_bias`` [n_experts] is added to the scores for the
         selection only; ``n_group`` > 1: group-limited routing with ``n_group_used`` groups (the
         parameters of the reference's ``moe_select``, src/locus/model/llama.cpp:900-980)."""
@@ -89,7 +123,12 @@ class SparseMoe(FeedForward):
         self.norm_topk, self.I, self.Is = bool(norm_topk), int(expert_intermediate), int(shared_intermediate)
         self.shared_gate = bool(shared_gate) and self.Is > 0
         self.weight_scale = float(weight_scale)
-        self.shared = (DenseMlp(prefix + ".shared_expert", hidden=hidden, intermediate=self.Is)
+        if activation not in ACTIVATIONS:
+            raise ValueError(f"sparse_moe: activation {activation!r} (known: {', '.join(ACTIVATIONS)})")
+        self.activation, self.has_router_bias = activation, bool(router_bias)
+        self.names = {**MOE_NAMES, **(names or {})}
+        self.shared = (DenseMlp(f"{prefix}.{self.names['shared']}", hidden=hidden, intermediate=self.Is,
+                                activation=activation, names=shared_names)
                        if self.Is > 0 else None)
         self._layout = None
         self._scratch = None
@@ -104,10 +143,13 @@ class SparseMoe(FeedForward):
     def param_shapes(self):
         s = {
             "router": (self.E, self.hidden),
-            "gate_exps": (self.E, self.I, self.hidden),
             "up_exps": (self.E, self.I, self.hidden),
             "down_exps": (self.E, self.hidden, self.I),
         }
+        if self.activation == "swiglu":
+            s["gate_exps"] = (self.E, self.I, self.hidden)
+        if self.has_router_bias:
+            s["router_bias"] = (self.E,)
         if self.shared_gate:
             s["shared_gate"] = (1, self.hidden)
         if self.has_sel_bias:
@@ -115,17 +157,20 @@ class SparseMoe(FeedForward):
         return s
 
     def sources(self):
-        p = self.prefix
-        out = [TensorSource(f"{p}.gate.weight", (self.E, self.hidden), "router")]
+        p, n = self.prefix, self.names
+        out = [TensorSource(f"{p}.{n['router']}", (self.E, self.hidden), "router")]
         for e in range(self.E):
-            out.append(TensorSource(f"{p}.experts.{e}.gate_proj.weight", (self.I, self.hidden), "gate_exps", e * self.I))
-            out.append(TensorSource(f"{p}.experts.{e}.up_proj.weight", (self.I, self.hidden), "up_exps", e * self.I))
-            out.append(TensorSource(f"{p}.experts.{e}.down_proj.weight", (self.hidden, self.I), "down_exps",
+            if self.activation == "swiglu":
+                out.append(TensorSource(f"{p}.{n['expert_gate'].format(e=e)}", (self.I, self.hidden), "gate_exps", e * self.I))
+            out.append(TensorSource(f"{p}.{n['expert_up'].format(e=e)}", (self.I, self.hidden), "up_exps", e * self.I))
+            out.append(TensorSource(f"{p}.{n['expert_down'].format(e=e)}", (self.hidden, self.I), "down_exps",
                                     e * self.hidden))
+        if self.has_router_bias:
+            out.append(TensorSource(f"{p}.{n['router_bias']}", (self.E,), "router_bias", 0, "bias"))
         if self.shared_gate:
-            out.append(TensorSource(f"{p}.shared_expert_gate.weight", (1, self.hidden), "shared_gate"))
+            out.append(TensorSource(f"{p}.{n['shared_gate']}", (1, self.hidden), "shared_gate"))
         if self.has_sel_bias:
-            out.append(TensorSource(f"{p}.gate.selection_bias", (self.E,), "sel_bias", 0, "bias"))
+            out.append(TensorSource(f"{p}.{n['selection_bias']}", (self.E,), "sel_bias", 0, "bias"))
         return out
 
     def kernel_modules(self, dtype):
@@ -145,15 +190,29 @@ class SparseMoe(FeedForward):
         self._rule = dict(top_k=self.k, renorm=self.norm_topk, scale=self.weight_scale, score_fn=self.score_fn,
                           sel_bias=bias.float().contiguous() if bias is not None else None, n_group=self.n_group,
                           n_group_used=self.n_group_used)
+        # the router's own bias as float32 over the logit rows (the gate's row, when there is one, gets none)
+        self._logit_bias = None
+        if self.has_router_bias:
+            lb = torch.zeros(self.E + 1, dtype=torch.float32, device=rt.device)
+            lb[: self.E] = self.params["router_bias"].float()
+            self._logit_bias = lb
         r, g = self.params["router"], self.params.get("shared_gate")
         if (rt.dtype == torch.bfloat16 and r.dtype == torch.bfloat16 and self.hidden % 8 == 0
                 and (g is None or g.dtype == torch.bfloat16)):
             # router rows and the gate row as one matrix (a copy of a few hundred KB)
             self._router_all = torch.cat([r, g.view(1, -1)], 0).contiguous() if g is not None else r
 
-    def forward(self, h, batch, residual, rt) -> None:
+    def _first_product(self, x, act, **kw) -> None:
+        if self.activation == "swiglu":
+            K.linear(x, self.params["gate_exps"], act, w2=self.params["up_exps"], **kw)
+        else:
+            K.linear(x, self.params["up_exps"], act, act="relu2", **kw)
+
+    def forward(self, h, batch, residual, rt, accumulate=True) -> None:
         T = h.shape[0]
         n_pairs = T * self.k
+        if not accumulate and self.shared is None:
+            residual.zero_()   # nothing else writes the rows before the experts' sum is added
         ids = rt.buf("moe.ids", (rt.max_tokens * self.k,), torch.int32)
         wts = rt.buf("moe.wts", (rt.max_tokens * self.k,), torch.float32)
         gamma = rt.buf("moe.gamma", (rt.max_tokens,), torch.float32) if self.shared_gate else None
@@ -161,7 +220,7 @@ class SparseMoe(FeedForward):
         # which kernels the expert products run on decides the row tile of the expert layout
         tile = K.FEW_ROWS if T <= K.FEW_ROWS else K.expert_tile(n_pairs, self.E)
         widths_ok = self.I % 8 == 0 and self.hidden % 8 == 0
-        all_bf16 = (K.tensor_cores_take(h, self.params["gate_exps"]) and widths_ok
+        all_bf16 = (K.tensor_cores_take(h, self.params["up_exps"]) and widths_ok
                     and self.params["down_exps"].dtype == torch.bfloat16)
         if not all_bf16 and widths_ok and n_pairs <= K.FEW_ROWS * self.E:
             # No tensor-core form (float32) and a handful of rows per expert: tiles of 8 rows on the row-streaming
@@ -192,14 +251,15 @@ class SparseMoe(FeedForward):
             if K.route_small_takes(T, self.k, self.E):
                 # a decode-sized batch: logits, selection and the expert layout in one launch
                 K.route_fused_small(h, self._router_all, logits, self.E, self.shared_gate, ids, wts, gamma, lay,
-                                    self._scratch.fused_counter, n_tokens=T, tile_m=tile, **self._rule)
+                                    self._scratch.fused_counter, n_tokens=T, tile_m=tile,
+                                    logit_bias=self._logit_bias, **self._rule)
                 sorted_already = True
             else:
-                K.router_logits(h, self._router_all, logits)
+                K.router_logits(h, self._router_all, logits, bias=self._logit_bias)
                 K.router_select(logits, self.E, self.shared_gate, ids, wts, gamma, n_tokens=T, **self._rule)
         else:
             K.router_topk(h, self.params["router"], self.params.get("shared_gate"), ids, wts, gamma,
-                          scratch=self._scratch, **self._rule)
+                          scratch=self._scratch, logit_bias=self._logit_bias, **self._rule)
         if self.observer is not None:
             self.observer(self.prefix, ids[:n_pairs].view(T, self.k), wts[:n_pairs].view(T, self.k))
         # The rest of the shared expert runs beside the routed experts on the side stream and is joined before the
@@ -207,9 +267,9 @@ class SparseMoe(FeedForward):
         if overlap:
             with rt.side():
                 if shared_act is not None:
-                    self.shared.forward_down(shared_act, residual, rt, row_scale=gamma)
+                    self.shared.forward_down(shared_act, residual, rt, row_scale=gamma, accumulate=accumulate)
                 else:
-                    self.shared.forward(h, batch, residual, rt, row_scale=gamma)
+                    self.shared.forward(h, batch, residual, rt, row_scale=gamma, accumulate=accumulate)
         act = rt.rows(f"moe.act{self.I}", self.I, rt.dtype, n_pairs, per_token=self.k)
         if not sorted_already:
             # the second product of the tensor-core path may walk the layout in larger tiles
@@ -217,13 +277,12 @@ class SparseMoe(FeedForward):
             K.moe_sort(ids, n_pairs, lay, tile, tile2)
         if streamed or not all_bf16:
             # few rows per expert (or no tensor-core form): the kernels gather the token rows themselves
-            K.linear(h, self.params["gate_exps"], act, w2=self.params["up_exps"], x_rows=lay.sorted_pair,
-                     x_row_div=self.k, layout=lay, n_rows=n_pairs)
+            self._first_product(h, act, x_rows=lay.sorted_pair, x_row_div=self.k, layout=lay, n_rows=n_pairs)
         else:
             # tcgen05 kernel: TMA reads whole row ranges, so lay the tokens out in expert order first
             xs = rt.rows("moe.x_sorted", self.hidden, rt.dtype, n_pairs, per_token=self.k)
             K.gather_rows(h, lay.sorted_pair, self.k, xs, n_pairs)
-            K.linear(xs, self.params["gate_exps"], act, w2=self.params["up_exps"], layout=lay, n_rows=n_pairs)
+            self._first_product(xs, act, layout=lay, n_rows=n_pairs)
         # the experts' weighted outputs, one row per (token, slot): in the model's element type (in bfloat16 a row is
         # rounded once more, like every activation between kernels; their sum, the residual stream, stays float32)
         pair_dt = torch.bfloat16 if (all_bf16 and rt.dtype == torch.bfloat16) else torch.float32
@@ -233,7 +292,7 @@ class SparseMoe(FeedForward):
         if overlap:
             rt.join()
         if self.shared is not None and not overlap:
-            self.shared.forward(h, batch, residual, rt, row_scale=gamma)
+            self.shared.forward(h, batch, residual, rt, row_scale=gamma, accumulate=accumulate)
         if rt.defer_add and K.rmsnorm_adds(residual):
             # the sum of the experts' outputs is folded into the next block's first norm
             rt.leave_pending(PendingAdd(pair_out, lay.pair_pos, self.k))

@@ -15,16 +15,18 @@ from .base import Norm, TensorSource, register_norm
 
 
 class RMSNorm(Norm):
-    def __init__(self, prefix: str, *, width: int, eps: float) -> None:
+    def __init__(self, prefix: str, *, width: int, eps: float, tensor: str = "") -> None:
+        """``tensor``: the checkpoint tensor's name where it is not ``<prefix>.weight``."""
         super().__init__(prefix)
         self.width = int(width)
         self.eps = float(eps)
+        self.tensor = str(tensor or prefix + ".weight")
 
     def param_shapes(self):
         return {"weight": (self.width,)}
 
     def sources(self):
-        return [TensorSource(self.prefix + ".weight", (self.width,), "weight", 0, "norm")]
+        return [TensorSource(self.tensor, (self.width,), "weight", 0, "norm")]
 
     def kernel_modules(self, dtype):
         return ["elementwise"]
@@ -35,6 +37,11 @@ class RMSNorm(Norm):
             add = None
         K.rmsnorm(x, self.params["weight"], self.eps, out, rows,
                   add=None if add is None else (add.pair_out, add.pair_pos, add.top_k))
+
+
+    def forward_add(self, y: torch.Tensor, x: torch.Tensor) -> None:
+        """x += norm(y): the norm of a sublayer's output (float32 rows) added to the residual stream."""
+        K.rmsnorm_add(y, self.params["weight"], self.eps, x)
 
 
 register_norm("rmsnorm", RMSNorm)

@@ -49,7 +49,8 @@ class ExpertLayout(K.ExpertLayout):
 
 def linear(x, w, out, *, w2=None, bias=None, accumulate=False, row_scale=None, scale_rows=None, x_rows=None, lists_ready=False,
            second_tiles=False,
-           x_row_div=1, layout=None, n_rows=None):
+           x_row_div=1, layout=None, n_rows=None, act=None):
+    assert act in (None, "relu2") and not (act and w2 is not None)
     M = out.shape[0] if n_rows is None else n_rows
     if M == 0:
         return
@@ -74,6 +75,8 @@ def linear(x, w, out, *, w2=None, bias=None, accumulate=False, row_scale=None, s
                 y[a:b] = ye
     if bias is not None:
         y = y + _f(bias)
+    if act == "relu2":
+        y = torch.clamp(y, min=0.0) ** 2
     if row_scale is not None:
         rs = row_scale[scale_rows[:M].long()] if scale_rows is not None else row_scale[:M]
         y = y * _f(rs)[:, None]
@@ -194,9 +197,11 @@ def _select(logits_row, top_k, renorm, scale, score_fn, sel_bias, n_group, n_gro
 
 
 def router_topk(h, w_router, w_gate, ids, wts, gamma, *, top_k, renorm, scale=1.0, scratch=None, score_fn="softmax",
-                sel_bias=None, n_group=1, n_group_used=1):
+                sel_bias=None, n_group=1, n_group_used=1, logit_bias=None):
     T = h.shape[0]
     r = _f(h) @ _f(w_router).T
+    if logit_bias is not None:
+        r = r + _f(logit_bias[: r.shape[1]])
     for t in range(T):
         picked, w = _select(r[t], top_k, renorm, scale, score_fn, sel_bias, n_group, n_group_used)
         for j, e in enumerate(picked):
@@ -207,9 +212,12 @@ def router_topk(h, w_router, w_gate, ids, wts, gamma, *, top_k, renorm, scale=1.
         gamma[:T] = (1.0 / (1.0 + torch.exp(-z))).to(gamma.dtype)
 
 
-def router_logits(h, w_all, logits):
+def router_logits(h, w_all, logits, bias=None):
     T, n = h.shape[0], w_all.shape[0]
-    logits[:T, :n] = (_f(h) @ _f(w_all).T).to(logits.dtype)
+    z = _f(h) @ _f(w_all).T
+    if bias is not None:
+        z = z + _f(bias[:n])
+    logits[:T, :n] = z.to(logits.dtype)
 
 
 def router_select(logits, n_experts, has_gate, ids, wts, gamma, *, n_tokens, top_k, renorm, scale=1.0,
@@ -237,8 +245,8 @@ def route_small(logits, n_experts, has_gate, ids, wts, gamma, layout, *, n_token
 
 
 def route_fused_small(h, w_all, logits, n_experts, has_gate, ids, wts, gamma, layout, counter, *, n_tokens, tile_m=None,
-                      **rule):
-    router_logits(h[:n_tokens], w_all, logits)
+                      logit_bias=None, **rule):
+    router_logits(h[:n_tokens], w_all, logits, bias=logit_bias)
     route_small(logits, n_experts, has_gate, ids, wts, gamma, layout, n_tokens=n_tokens, tile_m=tile_m, **rule)
 
 
@@ -336,8 +344,118 @@ def sample(logits, *, temperature, top_k, top_p, min_p, seeds, counters, out, ke
             kept_count[r] = int(keep.sum())
 
 
+def cast_rows(x, out):
+    out.copy_(x.to(out.dtype))
+
+
+def rmsnorm_add(y, w, eps, x):
+    ys = _f(y)
+    x += (ys / torch.sqrt((ys * ys).mean(-1, keepdim=True) + eps) * _f(w)).to(x.dtype)
+
+
+def _turn(x, positions, freq, magnitude, rot_pairs):
+    """x [T, ..., n]: interleaved pairs (2i, 2i + 1), i < rot_pairs, turned by positions[t] * freq[i]."""
+    if rot_pairs == 0:
+        return x
+    T = x.shape[0]
+    ang = positions[:T].to(torch.float64)[:, None] * freq[:rot_pairs].to(torch.float64)[None, :]
+    shape = [T] + [1] * (x.dim() - 2) + [rot_pairs]
+    c = (torch.cos(ang) * magnitude).to(x.dtype).view(shape)
+    s = (torch.sin(ang) * magnitude).to(x.dtype).view(shape)
+    out = x.clone()
+    u, v = x[..., 0:2 * rot_pairs:2], x[..., 1:2 * rot_pairs:2]
+    out[..., 0:2 * rot_pairs:2] = u * c - v * s
+    out[..., 1:2 * rot_pairs:2] = v * c + u * s
+    return out
+
+
+def latent_prep(dqkv, positions, freq, magnitude, w_q, w_kv, eps, cq_out, pool, slots, *, q_rank, kv_rank, rot_dim,
+                rot_pairs, write=True):
+    T = dqkv.shape[0]
+    x = _f(dqkv)
+
+    def unit(v):
+        return v / torch.sqrt((v * v).mean(-1, keepdim=True) + eps)
+
+    cq_out[:T] = (unit(x[:, :q_rank]) * _f(w_q)).to(cq_out.dtype)
+    if not write:
+        return
+    c = unit(x[:, q_rank:q_rank + kv_rank]) * _f(w_kv)
+    kr = _turn(x[:, q_rank + kv_rank:], positions, freq, magnitude, rot_pairs)
+    rows = torch.cat([c, kr], -1).to(pool.dtype)
+    page_tokens = pool.shape[-2]
+    for t in range(T):
+        pool[int(slots[t]) // page_tokens, 0, 0, int(slots[t]) % page_tokens] = rows[t]
+
+
+def latent_q_split(q, positions, freq, magnitude, q_nope_hm, q_rot, *, n_heads, nope_dim, rot_dim, rot_pairs):
+    T = q.shape[0]
+    x = _f(q).view(T, n_heads, nope_dim + rot_dim)
+    q_nope_hm[: n_heads * T] = x[..., :nope_dim].transpose(0, 1).reshape(n_heads * T, nope_dim).to(q_nope_hm.dtype)
+    q_rot[:T] = _turn(x[..., nope_dim:], positions, freq, magnitude, rot_pairs).reshape(T, -1).to(q_rot.dtype)
+
+
+def latent_attn(q_abs_hm, q_rot, pool, sink, out_hm, *, seg_q0, seg_qn, seg_ctx, block_table, items, n_items, n_tokens,
+                n_heads, kv_rank, rot_dim, page_tokens, window, scale):
+    T = n_tokens
+    done = set()
+    for it in range(n_items):
+        seg = int(items[it, 0])
+        if seg in done:
+            continue
+        done.add(seg)
+        q0, qn, ctx = int(seg_q0[seg]), int(seg_qn[seg]), int(seg_ctx[seg])
+        for i in range(qn):
+            p = ctx + i
+            lo = max(0, p - window + 1) if window > 0 else 0
+            pages = [int(block_table[seg, t // page_tokens]) for t in range(lo, p + 1)]
+            assert all(pg >= 0 for pg in pages), "latent attention reads a page that was given back"
+            rows = torch.stack([_f(pool[pg, 0, 0, t % page_tokens]) for pg, t in zip(pages, range(lo, p + 1))])
+            for h in range(n_heads):
+                qa = _f(q_abs_hm[h * T + q0 + i])
+                qr = _f(q_rot[q0 + i]).view(n_heads, rot_dim)[h]
+                s = (rows[:, :kv_rank] @ qa + rows[:, kv_rank:] @ qr) * scale
+                big = s.max() if sink is None else torch.maximum(s.max(), _f(sink)[h])
+                e = torch.exp(s - big)
+                den = e.sum() + (torch.exp(_f(sink)[h] - big) if sink is not None else 0.0)
+                out_hm[h * T + q0 + i] = ((e / den) @ rows[:, :kv_rank]).to(out_hm.dtype)
+
+
+def heads_to_rows(src_hm, out, *, n_tokens, n_heads):
+    d = src_hm.shape[1]
+    out[:n_tokens] = src_hm[: n_heads * n_tokens].view(n_heads, n_tokens, d).transpose(0, 1).reshape(n_tokens, n_heads * d)
+
+
+def retention_scan(qkvg, state, state_slots, seg_q0, seg_qn, n_seg, decay, k_scale, o_raw, *, n_heads, dim, v_dim):
+    H, d, dv = n_heads, dim, v_dim
+    for seg in range(n_seg):
+        q0, qn, slot = int(seg_q0[seg]), int(seg_qn[seg]), int(state_slots[seg])
+        S = _f(state[slot])
+        for t in range(q0, q0 + qn):
+            row = _f(qkvg[t])
+            q, k = row[: H * d].view(H, d), row[H * d:2 * H * d].view(H, d) * k_scale
+            v = row[2 * H * d:2 * H * d + H * dv].view(H, dv)
+            S = _f(decay).view(H, 1, 1) * S + k[:, :, None] * v[:, None, :]
+            o_raw[t] = torch.einsum("hdv,hd->hv", S, q).reshape(-1).to(o_raw.dtype)
+        state[slot] = S.to(state.dtype)
+
+
+def retention_gate_norm(o_raw, qkvg, gate_offset, eps, out, *, n_heads, v_dim):
+    T = out.shape[0]
+    o = _f(o_raw[:T]).view(T, n_heads, v_dim)
+    g = _f(qkvg[:T, gate_offset:gate_offset + n_heads * v_dim]).view(T, n_heads, v_dim)
+    unit = o / torch.sqrt((o * o).mean(-1, keepdim=True) + eps)
+    out[:T] = (unit * (g / (1.0 + torch.exp(-g)))).reshape(T, -1).to(out.dtype)
+
+
+def head_tile(n_tokens, dtype, widths_ok):
+    return 8 if (widths_ok and n_tokens <= 8) else 64
+
+
 _NAMES = ["embed_rows", "rmsnorm", "rmsnorm_adds", "attn_chunk_tc_takes", "linear", "rope_kv_write", "attn_chunk", "attn_chunk_mma", "attn_decode", "router_topk", "router_logits", "router_select",
-          "moe_sort", "route_small", "route_small_takes", "route_fused_small", "moe_combine", "gather_rows", "apply_penalties", "sample"]
+          "moe_sort", "route_small", "route_small_takes", "route_fused_small", "moe_combine", "gather_rows", "apply_penalties", "sample",
+          "cast_rows", "rmsnorm_add", "latent_prep", "latent_q_split", "latent_attn", "heads_to_rows", "retention_scan",
+          "retention_gate_norm", "head_tile"]
 
 
 def install(monkeypatch) -> None:
