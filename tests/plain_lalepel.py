@@ -168,12 +168,16 @@ def route(h: torch.Tensor, weights, prefix: str, top: int) -> Tuple[torch.Tensor
     return z, idx, torch.softmax(val, -1)
 
 
-def moe_ff(h: torch.Tensor, weights, prefix: str, mlp: dict, picks: Optional[torch.Tensor] = None) -> torch.Tensor:
+def moe_ff(h: torch.Tensor, weights, prefix: str, mlp: dict, picks: Optional[torch.Tensor] = None,
+           aux: Optional[dict] = None) -> torch.Tensor:
     """``picks`` [T, top]: use these experts instead of the router's own choice (the weights
-    are then the softmax over THEIR logits), for comparisons that must not hinge on a near-tie."""
+    are then the softmax over THEIR logits), for comparisons that must not hinge on a near-tie.
+    ``aux``: gets the router's logits under the prefix."""
     T = h.shape[0]
     top = int(mlp["router"]["top"])
     z, idx, wts = route(h, weights, prefix, top)
+    if aux is not None:
+        aux[prefix] = z
     if picks is not None:
         idx = picks.to(torch.int64)
         wts = torch.softmax(torch.gather(z, 1, idx), -1)
@@ -193,7 +197,7 @@ def moe_ff(h: torch.Tensor, weights, prefix: str, mlp: dict, picks: Optional[tor
 
 
 def forward(cfg: dict, weights, tokens: List[int], picks: Optional[Dict[str, torch.Tensor]] = None,
-            round_inputs=None) -> Tuple[torch.Tensor, List[torch.Tensor]]:
+            round_inputs=None, aux: Optional[dict] = None) -> Tuple[torch.Tensor, List[torch.Tensor]]:
     """Logits [T, vocab] of one sequence from position 0 on, and the residual stream behind every layer.
     ``round_inputs``: a function applied to what a sublayer reads (to mimic a 16-bit engine)."""
     eps = float(cfg["norm"]["eps"])
@@ -214,7 +218,7 @@ def forward(cfg: dict, weights, tokens: List[int], picks: Optional[Dict[str, tor
             if mlp["kind"] == "dense":
                 y = dense_ff(rd(x), weights, p + ".mlp")
             elif mlp["kind"] == "moe":
-                y = moe_ff(rd(x), weights, p + ".mlp", mlp, None if picks is None else picks.get(p + ".mlp"))
+                y = moe_ff(rd(x), weights, p + ".mlp", mlp, None if picks is None else picks.get(p + ".mlp"), aux)
             else:
                 raise ValueError(mlp["kind"])
             x = x + rmsnorm(y, _w(weights, p + ".norm2"), eps)
