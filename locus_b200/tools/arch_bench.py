@@ -1,0 +1,198 @@
+"""Prefill and decode throughput of the Lalepel design at layer sizes that resemble a real model's, beside the
+Qwen2-MoE architecture at equal sizes (random weights, synthetic token ids, one GPU).
+
+    python -m locus_b200.tools.arch_bench [--size m|s] [--layers 4] [--prefill 2048] [--batch 8] [--context 4096]
+                                          [--steps 16] [--warmup 3] [--dtype bf16|fp32] [--kernels]
+
+Both models get the same width, head count and head sizes, experts, picks per token, expert and shared widths and
+vocabulary; Lalepel's layers cycle through (latent attention, latent attention, retention, latent attention), all
+with routed experts.  Timed on the device with CUDA events after warm-up; every step reads its weights (several
+hundred MB: more than the L2 holds).  ``--kernels`` adds, for one eager prefill step and one eager decode step of
+each model, the time by kernel entry point, and for the mixers' own kernels what their bytes or flops would take
+at the measured peaks.  Prints one JSON line.
+"""
+from __future__ import annotations
+
+import argparse
+import json
+import os
+import sys
+
+SIZES = {
+    # width, heads, head size (Qwen) = unrotated + rotated (Lalepel), value size, ranks, experts
+    "m": dict(width=2048, heads=16, dim=128, rot=64, vdim=128, q_rank=768, kv_rank=512, window=4096, experts=60, top=4,
+              ff=1408, shared=5632, vocab=151936, ret_dim=128),
+    "s": dict(width=1024, heads=8, dim=64, rot=32, vdim=64, q_rank=384, kv_rank=256, window=1024, experts=32, top=2,
+              ff=704, shared=2816, vocab=32000, ret_dim=64),
+}
+
+
+def lalepel_config(z, n_layers):
+    moe = {"kind": "moe", "router": {"experts": z["experts"], "top": z["top"]}, "expert": {"ff": z["ff"]},
+           "shared": {"ff": z["shared"]}}
+    lat = {"type": "latent_attention", "mlp": moe, "mixer": {
+        "heads": z["heads"], "dim": z["dim"], "rot_dim": z["rot"], "vdim": z["vdim"], "q_rank": z["q_rank"],
+        "kv_rank": z["kv_rank"], "scale": (z["dim"] + z["rot"]) ** -0.5, "mask": {"size": z["window"]},
+        "rot": {"base": 10000.0, "dims": z["rot"], "scaling": {"factor": 8.0, "original": 4096, "fast": 32.0, "slow": 1.0}}}}
+    ret = {"type": "retention", "mlp": moe, "mixer": {
+        "heads": z["heads"], "dim": z["ret_dim"], "vdim": z["vdim"],
+        "decay": [1.0 - 2.0 ** (-5 - 0.5 * i) for i in range(z["heads"])]}}
+    return {"architecture": "Lalepel", "width": z["width"], "vocab": z["vocab"], "norm": {"eps": 1e-6},
+            "layers": [(ret if i % 4 == 2 else lat) for i in range(n_layers)]}
+
+
+def qwen_config(z, n_layers, max_pos):
+    hd = z["dim"] + z["rot"] if (z["dim"] + z["rot"]) in (64, 128) else z["dim"]
+    return {"architectures": ["Qwen2MoeForCausalLM"], "model_type": "qwen2_moe", "num_hidden_layers": n_layers,
+            "hidden_size": z["width"], "num_attention_heads": z["heads"], "num_key_value_heads": z["heads"],
+            "head_dim": z["dim"], "vocab_size": z["vocab"], "rope_theta": 1000000.0, "rms_norm_eps": 1e-6,
+            "max_position_embeddings": max_pos, "decoder_sparse_step": 1, "num_experts": z["experts"],
+            "num_experts_per_tok": z["top"], "norm_topk_prob": False, "moe_intermediate_size": z["ff"],
+            "shared_expert_intermediate_size": z["shared"], "intermediate_size": z["shared"], "qkv_bias": True,
+            "tie_word_embeddings": False, "use_sliding_window": False, "mlp_only_layers": [], "hidden_act": "silu",
+            "eos_token_id": -1, "_head": hd}
+
+
+def peaks():
+    path = os.path.join(os.path.dirname(os.path.dirname(os.path.dirname(os.path.abspath(__file__)))), "MEASURED_PEAKS.json")
+    if os.path.isfile(path):
+        with open(path) as f:
+            p = json.load(f)
+        return {"hbm_gbs": float(p["hbm_gbs"]), "bf16_tflops": float(p["bf16_tflops"]), "source": "measured"}
+    return {"hbm_gbs": 6650.0, "bf16_tflops": 1590.0, "source": "fallback"}
+
+
+def run(args) -> dict:
+    import torch
+
+    import locus_b200.kernels as K
+    import locus_b200.models  # noqa: F401
+    from locus_b200.cache import CacheManager
+    from locus_b200.config import arch_name_of, find_arch
+    from locus_b200.engine.step import ModelRunner, StepEntry
+    from locus_b200.models.model import Model
+    from locus_b200.weights.loader import RandomSource, load_weights
+
+    dev = "cuda:0"
+    torch.cuda.set_device(0)
+    z = SIZES[args.size]
+    dtype = torch.bfloat16 if args.dtype == "bf16" else torch.float32
+    el = 2 if dtype == torch.bfloat16 else 4
+    ctx, B, T = args.context, args.batch, args.prefill
+    W, steps = max(3, args.warmup), args.steps
+    pk = peaks()
+    gen = torch.Generator().manual_seed(5)
+    raws = {"lalepel": lalepel_config(z, args.layers), "qwen2_moe": qwen_config(z, args.layers, max(ctx, T) + 8)}
+    raws["qwen2_moe"].pop("_head")
+    out = {}
+    for name, raw in raws.items():
+        entry = find_arch(arch_name_of(raw))
+        cfg = entry.parse_config(raw)
+        model = Model(entry.build_plan(cfg), dtype, dev)
+        load_weights(model, RandomSource(model, 3, dtype, dev))
+        P = 64
+        n_pages = max(B * (-(-ctx // P) + 1), -(-T // P) + 1)
+        cache = CacheManager(model.cache_needs(), page_tokens=P, n_pages=n_pages, n_state_slots=max(B, 1),
+                             max_seq_tokens=max(ctx, T) + 8, dtype=dtype, device=dev)
+        for g in cache.groups:
+            g.pool.uniform_(-1.0, 1.0)
+        runner = ModelRunner(model, cache, max_tokens=max(T, B), max_segments=max(B, 1), max_wanted=max(B, 1),
+                             use_graphs=True)
+        V = model.plan.vocab_size
+
+        def ev():
+            return torch.cuda.Event(enable_timing=True)
+
+        prompt = torch.randint(0, V, (T,), generator=gen).tolist()
+
+        def prefill_once():
+            seq = cache.open("p")
+            assert cache.ensure_capacity(seq, T)
+            a, b = ev(), ev()
+            a.record()
+            runner.step([StepEntry(seq, prompt, [T - 1])])
+            b.record()
+            torch.cuda.synchronize()
+            cache.release(seq)
+            return a.elapsed_time(b)
+
+        pre = min([prefill_once() for _ in range(W + 3)][W:])
+        seqs = [cache.open(f"d{i}") for i in range(B)]
+        for s in seqs:
+            assert cache.adopt(s, ctx - steps - W - 1)
+        toks = torch.randint(0, V, (steps + W, B), generator=gen).tolist()
+
+        def decode_once(i):
+            for s in seqs:
+                assert cache.ensure_capacity(s, 1)
+            runner.step([StepEntry(s, [toks[i][j]], [0]) for j, s in enumerate(seqs)])
+
+        for i in range(W):
+            decode_once(i)
+        torch.cuda.synchronize()
+        a, b = ev(), ev()
+        a.record()
+        for i in range(W, W + steps):
+            decode_once(i)
+        b.record()
+        torch.cuda.synchronize()
+        dec = a.elapsed_time(b) / steps
+        res = {"weights_gb": model.param_bytes() / 1e9, "prefill_tokens": T, "prefill_ms": pre,
+               "prefill_tokens_per_s": T / pre * 1e3, "decode_batch": B, "decode_context": ctx, "decode_ms": dec,
+               "decode_tokens_per_s": B / dec * 1e3}
+        if args.kernels:
+            tables = {}
+            with K.kernel_times() as kt:
+                seq = cache.open("pk")
+                assert cache.ensure_capacity(seq, T)
+                runner.step([StepEntry(seq, prompt, [T - 1])])
+                tables["prefill"] = {k: [n, round(ms, 4)] for k, (n, ms) in sorted(kt.table().items())}
+                cache.release(seq)
+            with K.kernel_times() as kt:
+                for s in seqs:
+                    assert cache.ensure_capacity(s, 1)
+                runner.step([StepEntry(s, [toks[0][j]], [0]) for j, s in enumerate(seqs)])
+                tables["decode"] = {k: [n, round(ms, 4)] for k, (n, ms) in sorted(kt.table().items())}
+            res["kernel_ms"] = tables
+        runner.check_device_errors()
+        for s in seqs:
+            cache.release(s)
+        out[name] = res
+        del runner, cache, model
+        torch.cuda.empty_cache()
+    # what the mixers' own kernels have to do per layer, at the measured peaks
+    H, R = z["heads"], z["kv_rank"] + z["rot"]
+    keys_avg = sum(min(p + 1, z["window"]) for p in range(T)) / T
+    bounds = {
+        "latent_attn_prefill_us": 2.0 * T * keys_avg * H * (R + z["kv_rank"]) / (pk["bf16_tflops"] * 1e12) * 1e6,
+        "qwen_attn_prefill_us": 2.0 * T * (T + 1) / 2 * H * 2 * z["dim"] / (pk["bf16_tflops"] * 1e12) * 1e6,
+        "latent_attn_decode_us": B * min(ctx, z["window"]) * R * el / (pk["hbm_gbs"] * 1e9) * 1e6,
+        "qwen_attn_decode_us": B * ctx * 2 * H * z["dim"] * el / (pk["hbm_gbs"] * 1e9) * 1e6,
+        "retention_decode_us": B * H * z["ret_dim"] * z["vdim"] * 4 * 2 / (pk["hbm_gbs"] * 1e9) * 1e6,
+        "retention_prefill_us": (T * (4 * H * z["ret_dim"] + 3 * H * z["vdim"]) * 4) / (pk["hbm_gbs"] * 1e9) * 1e6,
+    }
+    return {"metric": f"prefill and decode tokens/s, Lalepel beside Qwen2-MoE at equal layer sizes ({args.size}, "
+                      f"{args.layers} layers, {args.dtype})",
+            "size": z, "layers": args.layers, "dtype": args.dtype, "data": "synthetic", "designs": out,
+            "bounds_per_layer": bounds, "peaks": pk,
+            "l2": "no flush: every step reads its weights, more than the 126 MB L2"}
+
+
+def main(argv=None) -> int:
+    ap = argparse.ArgumentParser(prog="arch_bench", description=__doc__.split("\n\n")[0])
+    ap.add_argument("--size", default="m", choices=sorted(SIZES))
+    ap.add_argument("--layers", type=int, default=4)
+    ap.add_argument("--prefill", type=int, default=2048)
+    ap.add_argument("--batch", type=int, default=8)
+    ap.add_argument("--context", type=int, default=4096)
+    ap.add_argument("--steps", type=int, default=16)
+    ap.add_argument("--warmup", type=int, default=3)
+    ap.add_argument("--dtype", default="bf16", choices=["bf16", "fp32"])
+    ap.add_argument("--kernels", action="store_true")
+    args = ap.parse_args(argv)
+    print(json.dumps(run(args)))
+    return 0
+
+
+if __name__ == "__main__":
+    sys.exit(main())
