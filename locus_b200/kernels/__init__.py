@@ -1251,6 +1251,86 @@ def latent_attn(q_abs_hm: torch.Tensor, q_rot: torch.Tensor, pool: torch.Tensor,
     _check(code, "latent_attn", f"(heads {n_heads}, latent {kv_rank} + {rot_dim})")
 
 
+LATENT_MMA_RANKS = (32, 64, 128, 256, 512)
+
+
+def latent_attn_mma_takes(dtype: torch.dtype, kv_rank: int, rot_dim: int) -> bool:
+    """Whether :func:`latent_attn_mma` takes this case: bfloat16, a latent of 32, 64, 128, 256 or 512 elements and a
+    rotated part that is a multiple of 16 (or none); everything else runs on :func:`latent_attn`."""
+    return (USE_TENSOR_CORES and dtype == torch.bfloat16 and kv_rank in LATENT_MMA_RANKS and rot_dim % 16 == 0)
+
+
+def latent_mma_head_shift(n_heads: int) -> int:
+    """log2 of the heads that share a block of :func:`latent_attn_mma` (its 64 rows are 64 >> shift queries times
+    1 << shift heads): the smallest power of two that holds all heads, at most 16, so that a tile of keys in shared
+    memory serves as many heads as possible and a block still holds several queries."""
+    shift = 0
+    while (1 << shift) < n_heads and shift < 4:
+        shift += 1
+    return shift
+
+
+LATENT_MMA_MAX_SPLITS = 16
+
+
+def latent_attn_mma_splits(n_items: int, n_heads: int, head_shift: int, max_keys: int) -> int:
+    """Ranges the key tiles of every block of :func:`latent_attn_mma` are cut into: a step of single tokens (or of a
+    short portion) behind long contexts makes a handful of blocks that would each walk all keys alone; then the keys
+    are cut so that about every SM has a block, down to two tiles of 32 keys per range."""
+    blocks = n_items * (-(-n_heads // (1 << head_shift)))
+    tiles = -(-max_keys // 32)
+    n_sm = _sm_count()
+    if 2 * blocks > n_sm or tiles < 4:
+        return 1
+    return max(1, min(LATENT_MMA_MAX_SPLITS, n_sm // blocks, tiles // 2))
+
+
+def latent_attn_mma_scratch(kv_rank: int) -> Tuple[int, int]:
+    """Floats of the two scratch buffers (sums; maxima and denominators) for any cut that
+    :func:`latent_attn_mma_splits` chooses: the ranges of a step never outnumber the SMs."""
+    return _sm_count() * 64 * kv_rank, _sm_count() * 64 * 2
+
+
+def latent_attn_mma(q_abs_hm: torch.Tensor, q_rot: torch.Tensor, pool: torch.Tensor, sink: Optional[torch.Tensor],
+                    out_hm: torch.Tensor, *, seg_q0: torch.Tensor, seg_qn: torch.Tensor, seg_ctx: torch.Tensor,
+                    block_table: torch.Tensor, items: torch.Tensor, n_items: int, n_tokens: int, n_heads: int,
+                    kv_rank: int, rot_dim: int, page_tokens: int, window: int, scale: float, head_shift: int,
+                    n_splits: int = 1, part_o: Optional[torch.Tensor] = None,
+                    part_ml: Optional[torch.Tensor] = None) -> None:
+    """:func:`latent_attn` on the tensor cores (bfloat16): same arguments and result, but ``items`` lists tiles of
+    ``64 >> head_shift`` queries (:func:`latent_mma_head_shift`).  ``n_splits`` > 1
+    (:func:`latent_attn_mma_splits`) with scratch of :func:`latent_attn_mma_scratch` floats: every block's keys are
+    cut into that many ranges, merged in ascending order by a second kernel."""
+    if n_splits > 1:
+        units = n_items * (-(-n_heads // (1 << head_shift))) * n_splits
+        _need(part_o is not None and part_ml is not None and part_o.dtype == part_ml.dtype == torch.float32
+              and part_o.is_cuda and part_ml.is_cuda and part_o.numel() >= units * 64 * kv_rank
+              and part_ml.numel() >= units * 128, "latent_attn_mma: scratch too small for these ranges")
+    _cuda_c(q_abs_hm, "q_abs_hm")
+    _cuda_c(q_rot, "q_rot")
+    _cuda_c(pool, "pool")
+    _cuda_c(out_hm, "out_hm")
+    _i32(block_table, "block_table")
+    _i32(items, "items")
+    T = n_tokens
+    _need(q_abs_hm.dtype == q_rot.dtype == pool.dtype == out_hm.dtype == torch.bfloat16, "latent_attn_mma: bfloat16 only")
+    _need(q_abs_hm.shape[0] >= n_heads * T and q_abs_hm.shape[1] == kv_rank and out_hm.shape[0] >= n_heads * T
+          and out_hm.shape[1] == kv_rank and q_rot.shape[0] >= T and q_rot.shape[1] == n_heads * rot_dim,
+          "latent_attn_mma: shapes")
+    _need(pool.shape[-1] == kv_rank + rot_dim and pool.shape[-2] == page_tokens, "latent_attn_mma: pool layout")
+    if sink is not None:
+        _need(sink.is_cuda and sink.dtype == torch.float32 and sink.numel() == n_heads and sink.is_contiguous(),
+              "latent_attn_mma: sink must be float32 [H]")
+    code = _lib("latent_attention").locus_latent_attn_mma(
+        _p(q_abs_hm), _p(q_rot), _p(pool), _p(sink), _p(out_hm), _p(seg_q0), _p(seg_qn), _p(seg_ctx), _p(block_table),
+        I(block_table.shape[1]), _p(items), I(n_items), I(T), I(n_heads), I(kv_rank), I(rot_dim), I(page_tokens),
+        I(window), F(scale), I(head_shift), I(n_splits), _p(part_o if n_splits > 1 else None),
+        _p(part_ml if n_splits > 1 else None), _stream())
+    if n_splits > 1 and code == 0:
+        _count_launches(1)
+    _check(code, "latent_attn_mma", f"(heads {n_heads}, latent {kv_rank} + {rot_dim})")
+
+
 def heads_to_rows(src_hm: torch.Tensor, out: torch.Tensor, *, n_tokens: int, n_heads: int) -> None:
     """``src_hm`` [H * T, d] head-major -> ``out`` [T, H * d]."""
     _cuda_c(src_hm, "src_hm")

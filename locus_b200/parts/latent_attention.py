@@ -31,22 +31,22 @@ from .base import Mixer, PagedKvSpec, PartSpec, StepPlan, TensorSource, make_par
 
 
 class LatentTiles(StepPlan):
-    """Work items of ``latent_attn``: tiles of ``K.LATENT_QUERY_TILE`` queries over every segment, one token or
-    many, ordered by the position of their first query (the kernel walks the list from its end, so the tiles
+    """Work items of the latent attention kernels: tiles of ``tile`` queries over every segment, one token or
+    many, ordered by the position of their first query (the kernels walk the list from its end, so the tiles
     with the most keys start first)."""
 
-    key = ("latent_attention.tiles", K.LATENT_QUERY_TILE)
-
-    def __init__(self) -> None:
+    def __init__(self, tile: int = K.LATENT_QUERY_TILE) -> None:
         from ..cache import native
 
         self._lib = native.lib()
+        self.tile = int(tile)
+        self.key = ("latent_attention.tiles", self.tile)
 
     def capacity(self, max_tokens: int, max_segments: int) -> int:
-        return 2 * (max_tokens // K.LATENT_QUERY_TILE + max_segments)
+        return 2 * (max_tokens // self.tile + max_segments)
 
     def build(self, seg_q0, seg_qn, seg_ctx, out):
-        n = self._lib.locus_plan_query_tiles(len(seg_qn), seg_qn.ctypes.data, K.LATENT_QUERY_TILE, 1,
+        n = self._lib.locus_plan_query_tiles(len(seg_qn), seg_qn.ctypes.data, self.tile, 1,
                                              out.ctypes.data, len(out))
         if n < 0:
             raise ValueError("latent attention: the step has more query tiles than the plan's capacity holds")
@@ -140,7 +140,16 @@ class LatentAttention(Mixer):
         return PagedKvSpec(1, self.row, self.window, has_v=False), None
 
     def step_plans(self):
-        return [LatentTiles(), self._head_tiles]
+        return [self._query_tiles, self._head_tiles]
+
+    @property
+    def _query_tiles(self) -> LatentTiles:
+        """Tiles of 16 queries for the CUDA-core kernel, or of 64 / (heads that share a block) for the tensor-core
+        kernel where it takes this mixer's sizes."""
+        dtype = getattr(self, "_dtype", torch.float32)
+        self._mma = K.latent_attn_mma_takes(dtype, self.kv_rank, self.dr)
+        self._head_shift = K.latent_mma_head_shift(self.H)
+        return LatentTiles(64 >> self._head_shift if self._mma else K.LATENT_QUERY_TILE)
 
     @property
     def _head_tiles(self) -> HeadTiles:
@@ -157,6 +166,7 @@ class LatentAttention(Mixer):
         self._w_uv = self.params["w_uv"].view(self.H, self.dv, self.kv_rank)
         self._sink = self.params["sink"].float().contiguous() if self.has_sink else None
         self._gq, self._gkv = self.params["g_q"], self.params["g_kv"]
+        self._tiles_key = self._query_tiles.key   # also settles which attention kernel this mixer runs
 
     # -- forward ------------------------------------------------------------
     def forward(self, h, batch, cache, residual, rt, accumulate=True) -> None:
@@ -184,11 +194,26 @@ class LatentAttention(Mixer):
         q_abs = rt.rows(f"latent.q_abs{self.kv_rank}", self.kv_rank, rt.dtype, H * T, per_token=H)
         K.linear(q_nope, self._w_uk_t, q_abs, layout=lay, n_rows=H * T, lists_ready=True)
         o_lat = rt.rows(f"latent.o_lat{self.kv_rank}", self.kv_rank, rt.dtype, H * T, per_token=H)
-        tiles = batch.plans[LatentTiles.key]
-        K.latent_attn(q_abs, q_rot, cache.pool, self._sink, o_lat, seg_q0=batch.seg_q0, seg_qn=batch.seg_qn,
-                      seg_ctx=batch.seg_ctx, block_table=gb.block_table, items=tiles["items"],
-                      n_items=tiles["n_items"], n_tokens=T, n_heads=H, kv_rank=self.kv_rank, rot_dim=self.dr,
-                      page_tokens=gb.page_tokens, window=self.window, scale=self.scale)
+        tiles = batch.plans[self._tiles_key]
+        common = dict(seg_q0=batch.seg_q0, seg_qn=batch.seg_qn, seg_ctx=batch.seg_ctx, block_table=gb.block_table,
+                      items=tiles["items"], n_items=tiles["n_items"], n_tokens=T, n_heads=H, kv_rank=self.kv_rank,
+                      rot_dim=self.dr, page_tokens=gb.page_tokens, window=self.window, scale=self.scale)
+        if self._mma:
+            # the most keys a query of this step sees (all that the block table can describe when the step's
+            # launches must not depend on its lengths)
+            keys = gb.block_table.shape[1] * gb.page_tokens if batch.static_shapes else max(batch.longest, 1)
+            if self.window > 0:
+                keys = min(keys, self.window + (64 >> self._head_shift))
+            n_splits = K.latent_attn_mma_splits(tiles["n_items"], H, self._head_shift, keys)
+            part_o = part_ml = None
+            if n_splits > 1:
+                n_o, n_ml = K.latent_attn_mma_scratch(self.kv_rank)
+                part_o = rt.buf("latent.part_o", (n_o,), torch.float32)
+                part_ml = rt.buf("latent.part_ml", (n_ml,), torch.float32)
+            K.latent_attn_mma(q_abs, q_rot, cache.pool, self._sink, o_lat, head_shift=self._head_shift,
+                              n_splits=n_splits, part_o=part_o, part_ml=part_ml, **common)
+        else:
+            K.latent_attn(q_abs, q_rot, cache.pool, self._sink, o_lat, **common)
         o_hm = rt.rows(f"latent.o_hm{self.dv}", self.dv, rt.dtype, H * T, per_token=H)
         K.linear(o_lat, self._w_uv, o_hm, layout=lay, n_rows=H * T, lists_ready=True)
         o = rt.rows("latent.o", H * self.dv, rt.dtype, T)

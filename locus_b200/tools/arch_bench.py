@@ -91,12 +91,12 @@ def run(args) -> dict:
         model = Model(entry.build_plan(cfg), dtype, dev)
         load_weights(model, RandomSource(model, 3, dtype, dev))
         P = 64
-        n_pages = max(B * (-(-ctx // P) + 1), -(-T // P) + 1)
-        cache = CacheManager(model.cache_needs(), page_tokens=P, n_pages=n_pages, n_state_slots=max(B, 1),
+        n_pages = B * (-(-ctx // P) + 1) + -(-T // P) + 1
+        cache = CacheManager(model.cache_needs(), page_tokens=P, n_pages=n_pages, n_state_slots=B + 1,
                              max_seq_tokens=max(ctx, T) + 8, dtype=dtype, device=dev)
         for g in cache.groups:
             g.pool.uniform_(-1.0, 1.0)
-        runner = ModelRunner(model, cache, max_tokens=max(T, B), max_segments=max(B, 1), max_wanted=max(B, 1),
+        runner = ModelRunner(model, cache, max_tokens=max(T, B), max_segments=B + 1, max_wanted=B + 1,
                              use_graphs=True)
         V = model.plan.vocab_size
 

@@ -421,6 +421,10 @@ def latent_attn(q_abs_hm, q_rot, pool, sink, out_hm, *, seg_q0, seg_qn, seg_ctx,
                 out_hm[h * T + q0 + i] = ((e / den) @ rows[:, :kv_rank]).to(out_hm.dtype)
 
 
+def latent_attn_mma_takes(dtype, kv_rank, rot_dim):
+    return False
+
+
 def heads_to_rows(src_hm, out, *, n_tokens, n_heads):
     d = src_hm.shape[1]
     out[:n_tokens] = src_hm[: n_heads * n_tokens].view(n_heads, n_tokens, d).transpose(0, 1).reshape(n_tokens, n_heads * d)
@@ -455,7 +459,7 @@ def head_tile(n_tokens, dtype, widths_ok):
 _NAMES = ["embed_rows", "rmsnorm", "rmsnorm_adds", "attn_chunk_tc_takes", "linear", "rope_kv_write", "attn_chunk", "attn_chunk_mma", "attn_decode", "router_topk", "router_logits", "router_select",
           "moe_sort", "route_small", "route_small_takes", "route_fused_small", "moe_combine", "gather_rows", "apply_penalties", "sample",
           "cast_rows", "rmsnorm_add", "latent_prep", "latent_q_split", "latent_attn", "heads_to_rows", "retention_scan",
-          "retention_gate_norm", "head_tile"]
+          "retention_gate_norm", "head_tile", "latent_attn_mma_takes"]
 
 
 def install(monkeypatch) -> None:

@@ -64,11 +64,17 @@ CONFIGS = {
         with_mlp(latent(5, 4, 2, 6, 12, 12, window=70), None),
     ], eps=1e-6),
     # one layer each: a mechanism alone
-    "latent_only": model(48, 50, [with_mlp(latent(4, 8, 8, 8, 16, 24, window=20, scaling=SCALING), None)]),
+    "latent_only": model(48, 50, [with_mlp(latent(4, 8, 16, 8, 16, 32, window=20, scaling=SCALING), None)]),
     "latent_full": model(48, 50, [with_mlp(latent(2, 16, 0, 8, 32, 40, rot_dims=0), None)]),
     "retention_only": model(48, 50, [with_mlp(retention(2, 24, 16, [0.95, 0.999]), None)]),
     "dense_only": model(40, 50, [with_mlp(retention(1, 8, 8, [0.9]), DENSE(72))]),
     "moe_only": model(40, 50, [with_mlp(retention(1, 8, 8, [0.9]), MOE(7, 3, 16, shared=24))]),
+    # no routed layer: a window, a state and a layer that sees every key
+    "no_router": model(64, 83, [
+        with_mlp(latent(2, 16, 16, 16, 24, 32, window=24, scaling=SCALING), DENSE(64)),
+        with_mlp(retention(2, 16, 16, [0.97, 0.9995]), DENSE(48)),
+        with_mlp(latent(3, 8, 8, 8, 16, 16, base=300.0), None),
+    ]),
     # larger heads: latent rows of 160 elements, state rows beyond one lane's first register
     "wide": model(128, 211, [
         with_mlp(latent(4, 32, 32, 32, 64, 128, window=100, scaling={"factor": 8.0, "original": 256, "fast": 32.0, "slow": 1.0}), DENSE(256)),
