@@ -13,6 +13,8 @@
 //                        (up to 8 rows: d <= 256); per token one butterfly sum per column.  The order of every
 //                        sum is fixed by d alone, so a token's output does not depend on how the request's
 //                        tokens were cut into steps or on what else the step holds.
+//   retention_chunked    the same recurrence for long portions, a chunk of 32 tokens at a time as small matrix
+//                        products (see there)
 //   retention_gate_norm  out[t, h, :] = o[t, h, :] / rms(o[t, h, :]) * silu(g[t, h, :])   (a warp per row and head)
 #include "common.cuh"
 
@@ -22,13 +24,14 @@ template <int RPL>
 __global__ void __launch_bounds__(128) retention_scan_kernel(
     const float* __restrict__ qkvg, int ld, float* __restrict__ state, const int* __restrict__ state_slots,
     const int* __restrict__ seg_q0, const int* __restrict__ seg_qn, const float* __restrict__ decay, float k_scale,
-    float* __restrict__ o_raw, int H, int d, int dv, int col_groups) {
+    float* __restrict__ o_raw, int H, int d, int dv, int col_groups, int qn_below) {
     pdl_entry();
     pdl_trigger();
     const int lane = threadIdx.x & 31;
     const int unit = blockIdx.x * 4 + (threadIdx.x >> 5);  // (head, column group)
     const int seg = blockIdx.y;
     if (unit >= H * col_groups) return;
+    if (qn_below > 0 && seg_qn[seg] >= qn_below) return;  // a long portion: the chunked kernel's
     const int h = unit / col_groups, c0 = (unit % col_groups) * RET_CW;
     const int q0 = seg_q0[seg], qn = seg_qn[seg];
     float* S = state + (static_cast<size_t>(state_slots[seg]) * H + h) * d * dv;
@@ -95,10 +98,12 @@ __global__ void __launch_bounds__(128) retention_scan_kernel(
 }
 
 // qkvg [T, ld] float32 with the columns [q | k | v | g]; state [n_slots, H, d, dv] float32; decay [H] float32;
-// o_raw [T, H * dv] float32.  d <= 256.
+// o_raw [T, H * dv] float32.  d <= 256.  qn_below > 0: only the segments with fewer new tokens than that (the
+// others are locus_retention_chunked's).
 extern "C" int locus_retention_scan(const float* qkvg, int ld, float* state, const int* state_slots,
                                     const int* seg_q0, const int* seg_qn, int n_seg, const float* decay,
-                                    float k_scale, float* o_raw, int H, int d, int dv, cudaStream_t stream) {
+                                    float k_scale, float* o_raw, int H, int d, int dv, int qn_below,
+                                    cudaStream_t stream) {
     if (n_seg <= 0) return 0;
     if (H <= 0 || d <= 0 || d > 256 || dv <= 0 || n_seg > 65535 || ld < 2 * H * d + 2 * H * dv) return LOCUS_ERR_UNSUPPORTED;
     const int col_groups = (dv + RET_CW - 1) / RET_CW;
@@ -106,12 +111,134 @@ extern "C" int locus_retention_scan(const float* qkvg, int ld, float* state, con
     const int rpl = (d + 31) / 32;
 #define SCAN(R)                                                                                                 \
     locus_launch(retention_scan_kernel<R>, grid, dim3(128), 0, stream, qkvg, ld, state, state_slots, seg_q0,    \
-                 seg_qn, decay, k_scale, o_raw, H, d, dv, col_groups)
+                 seg_qn, decay, k_scale, o_raw, H, d, dv, col_groups, qn_below)
     if (rpl <= 1) SCAN(1);
     else if (rpl <= 2) SCAN(2);
     else if (rpl <= 4) SCAN(4);
     else SCAN(8);
 #undef SCAN
+    return locus_launch_status();
+}
+
+// ---------------------------------------------------------------------------
+// Long portions, chunk by chunk: with the tokens of a chunk of C = 32 as rows of Q, K (scaled) and V,
+//
+//     O = (Q K^T * D) V + diag(decay^(i+1)) Q S,        D[i][j] = decay^(i-j) for j <= i, else 0
+//     S <- decay^n S + (K * decay^(n-1-j))^T V          (n: the chunk's tokens)
+//
+// which is the recurrence above summed in another order (float32 FMAs on the CUDA cores; the powers of the decay by
+// repeated multiplication).  A block owns RC_COLS columns of one head's state for one request, keeps them in shared
+// memory across the request's chunks, and only the state couples a chunk to the next.
+#define RC_CHUNK 32
+#define RC_COLS 32
+
+__global__ void __launch_bounds__(256) retention_chunked_kernel(
+    const float* __restrict__ qkvg, int ld, float* __restrict__ state, const int* __restrict__ state_slots,
+    const int* __restrict__ seg_q0, const int* __restrict__ seg_qn, const float* __restrict__ decay, float k_scale,
+    float* __restrict__ o_raw, int H, int d, int dv, int col_groups, int qn_from) {
+    extern __shared__ float rc_smem[];
+    pdl_entry();
+    pdl_trigger();
+    const int seg = blockIdx.y;
+    const int qn = seg_qn[seg];
+    if (qn < qn_from) return;  // a short portion or a single token: the scan kernel's
+    const int h = blockIdx.x / col_groups, c0 = (blockIdx.x % col_groups) * RC_COLS;
+    const int q0 = seg_q0[seg];
+    const int ldq = d + 1;
+    float* Qs = rc_smem;                      // [C][d + 1]
+    float* Ks = Qs + RC_CHUNK * ldq;          // [C][d + 1]
+    float* Vs = Ks + RC_CHUNK * ldq;          // [C][RC_COLS]
+    float* As = Vs + RC_CHUNK * RC_COLS;      // [C][C + 1]
+    float* Ss = As + RC_CHUNK * (RC_CHUNK + 1);  // [d][RC_COLS]
+    float* pw = Ss + d * RC_COLS;             // [C + 1] powers of the decay
+    const int tid = threadIdx.x, lane = tid & 31, wid = tid >> 5;
+    const float lam = decay[h];
+    float* S = state + (static_cast<size_t>(state_slots[seg]) * H + h) * d * dv;
+    for (int i = tid; i < d * RC_COLS; i += 256) {
+        const int r = i / RC_COLS, c = i % RC_COLS;
+        Ss[i] = c0 + c < dv ? S[static_cast<size_t>(r) * dv + c0 + c] : 0.f;
+    }
+    if (tid == 0) {
+        float p = 1.f;
+        for (int n = 0; n <= RC_CHUNK; ++n) {
+            pw[n] = p;
+            p *= lam;
+        }
+    }
+    const int off_q = h * d, off_k = H * d + h * d, off_v = 2 * H * d + h * dv + c0;
+    for (int t0 = 0; t0 < qn; t0 += RC_CHUNK) {
+        const int n = min(RC_CHUNK, qn - t0);
+        __syncthreads();  // the state and the last chunk's operands are free
+        for (int i = tid; i < RC_CHUNK * d; i += 256) {
+            const int j = i / d, r = i % d;
+            const float* row = qkvg + static_cast<size_t>(q0 + t0 + j) * ld;
+            Qs[j * ldq + r] = j < n ? row[off_q + r] : 0.f;
+            Ks[j * ldq + r] = j < n ? row[off_k + r] * k_scale : 0.f;
+        }
+        for (int i = tid; i < RC_CHUNK * RC_COLS; i += 256) {
+            const int j = i / RC_COLS, c = i % RC_COLS;
+            Vs[i] = (j < n && c0 + c < dv) ? qkvg[static_cast<size_t>(q0 + t0 + j) * ld + off_v + c] : 0.f;
+        }
+        __syncthreads();
+        // A = (Q K^T) * D: row i = wid + 8 u, column j = lane
+#pragma unroll
+        for (int u = 0; u < RC_CHUNK / 8; ++u) {
+            const int i = wid + 8 * u, j = lane;
+            float dot = 0.f;
+            if (j <= i) {
+                const float* qr = Qs + i * ldq;
+                const float* kr = Ks + j * ldq;
+                for (int r = 0; r < d; ++r) dot = fmaf(qr[r], kr[r], dot);
+                dot *= pw[i - j];
+            }
+            As[i * (RC_CHUNK + 1) + j] = dot;
+        }
+        __syncthreads();
+        // O = A V + decay^(i+1) Q S: row i = wid + 8 u, column c = lane
+#pragma unroll
+        for (int u = 0; u < RC_CHUNK / 8; ++u) {
+            const int i = wid + 8 * u;
+            if (i >= n) continue;
+            float intra = 0.f, inter = 0.f;
+            const float* ar = As + i * (RC_CHUNK + 1);
+            for (int j = 0; j <= i; ++j) intra = fmaf(ar[j], Vs[j * RC_COLS + lane], intra);
+            const float* qr = Qs + i * ldq;
+            for (int r = 0; r < d; ++r) inter = fmaf(qr[r], Ss[r * RC_COLS + lane], inter);
+            if (c0 + lane < dv)
+                o_raw[static_cast<size_t>(q0 + t0 + i) * H * dv + h * dv + c0 + lane] = fmaf(pw[i + 1], inter, intra);
+        }
+        __syncthreads();
+        // S <- decay^n S + (K * decay^(n-1-j))^T V: row r = wid + 8 u, column c = lane
+        for (int r = wid; r < d; r += 8) {
+            float acc = 0.f;
+            for (int j = 0; j < n; ++j) acc = fmaf(Ks[j * ldq + r] * pw[n - 1 - j], Vs[j * RC_COLS + lane], acc);
+            Ss[r * RC_COLS + lane] = fmaf(pw[n], Ss[r * RC_COLS + lane], acc);
+        }
+    }
+    __syncthreads();
+    for (int i = tid; i < d * RC_COLS; i += 256) {
+        const int r = i / RC_COLS, c = i % RC_COLS;
+        if (c0 + c < dv) S[static_cast<size_t>(r) * dv + c0 + c] = Ss[i];
+    }
+}
+
+// The segments with at least qn_from new tokens (arguments as locus_retention_scan).
+extern "C" int locus_retention_chunked(const float* qkvg, int ld, float* state, const int* state_slots,
+                                       const int* seg_q0, const int* seg_qn, int n_seg, const float* decay,
+                                       float k_scale, float* o_raw, int H, int d, int dv, int qn_from,
+                                       cudaStream_t stream) {
+    if (n_seg <= 0) return 0;
+    if (H <= 0 || d <= 0 || d > 256 || dv <= 0 || n_seg > 65535 || ld < 2 * H * d + 2 * H * dv || qn_from < 1)
+        return LOCUS_ERR_UNSUPPORTED;
+    const int col_groups = (dv + RC_COLS - 1) / RC_COLS;
+    const size_t smem = sizeof(float) * (2 * RC_CHUNK * (d + 1) + RC_CHUNK * RC_COLS + RC_CHUNK * (RC_CHUNK + 1) +
+                                         static_cast<size_t>(d) * RC_COLS + RC_CHUNK + 1);
+    if (smem > 48 * 1024 &&
+        cudaFuncSetAttribute(retention_chunked_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                             static_cast<int>(smem)) != cudaSuccess)
+        return LOCUS_ERR_UNSUPPORTED;
+    locus_launch(retention_chunked_kernel, dim3(H * col_groups, n_seg), dim3(256), smem, stream, qkvg, ld, state,
+                 state_slots, seg_q0, seg_qn, decay, k_scale, o_raw, H, d, dv, col_groups, qn_from);
     return locus_launch_status();
 }
 

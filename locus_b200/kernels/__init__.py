@@ -1373,12 +1373,19 @@ def head_tile(n_tokens: int, dtype: torch.dtype, widths_ok: bool) -> int:
 RETENTION_MAX_DIM = 256
 
 
+RETENTION_CHUNK_FROM = 16   # segments with at least this many new tokens go to the chunked kernel
+
+
 def retention_scan(qkvg: torch.Tensor, state: torch.Tensor, state_slots: torch.Tensor, seg_q0: torch.Tensor,
                    seg_qn: torch.Tensor, n_seg: int, decay: torch.Tensor, k_scale: float, o_raw: torch.Tensor, *,
-                   n_heads: int, dim: int, v_dim: int) -> None:
+                   n_heads: int, dim: int, v_dim: int, short: bool = True, long: bool = True) -> None:
     """The recurrence S = decay[h] * S + (k * k_scale) v^T, o = S^T q over every segment's new tokens in order,
     from and into ``state`` [n_slots, H, dim, v_dim] (float32) of the segment's slot.  ``qkvg`` [T, >= 2 H dim +
-    2 H v_dim] float32 with the columns [q | k | v | gate]; ``o_raw`` [T, H * v_dim] float32."""
+    2 H v_dim] float32 with the columns [q | k | v | gate]; ``o_raw`` [T, H * v_dim] float32.
+
+    Two kernels share the segments: those with fewer than ``RETENTION_CHUNK_FROM`` new tokens are walked token by
+    token (a warp per few columns of the state), the longer ones chunk by chunk as small matrix products; ``short``
+    / ``long`` say whether the step has segments of either kind at all (both True when the host cannot know)."""
     _cuda_c(qkvg, "qkvg")
     _cuda_c(state, "state")
     _cuda_c(o_raw, "o_raw")
@@ -1387,10 +1394,16 @@ def retention_scan(qkvg: torch.Tensor, state: torch.Tensor, state_slots: torch.T
     _need(tuple(state.shape[1:]) == (n_heads, dim, v_dim) and decay.numel() == n_heads and decay.is_cuda,
           "retention_scan: state [slots, H, dim, v_dim], decay [H]")
     _need(o_raw.shape[1] == n_heads * v_dim and o_raw.shape[0] >= qkvg.shape[0], "retention_scan: o_raw")
-    code = _lib("retention").locus_retention_scan(
-        _p(qkvg), I(qkvg.stride(0)), _p(state), _p(state_slots), _p(seg_q0), _p(seg_qn), I(n_seg), _p(decay),
-        F(k_scale), _p(o_raw), I(n_heads), I(dim), I(v_dim), _stream())
-    _check(code, "retention_scan", f"(heads {n_heads}, dim {dim}, v_dim {v_dim})")
+    if short:
+        code = _lib("retention").locus_retention_scan(
+            _p(qkvg), I(qkvg.stride(0)), _p(state), _p(state_slots), _p(seg_q0), _p(seg_qn), I(n_seg), _p(decay),
+            F(k_scale), _p(o_raw), I(n_heads), I(dim), I(v_dim), I(RETENTION_CHUNK_FROM if long else 0), _stream())
+        _check(code, "retention_scan", f"(heads {n_heads}, dim {dim}, v_dim {v_dim})")
+    if long:
+        code = _lib("retention").locus_retention_chunked(
+            _p(qkvg), I(qkvg.stride(0)), _p(state), _p(state_slots), _p(seg_q0), _p(seg_qn), I(n_seg), _p(decay),
+            F(k_scale), _p(o_raw), I(n_heads), I(dim), I(v_dim), I(RETENTION_CHUNK_FROM if short else 1), _stream())
+        _check(code, "retention_chunked", f"(heads {n_heads}, dim {dim}, v_dim {v_dim})")
 
 
 def retention_gate_norm(o_raw: torch.Tensor, qkvg: torch.Tensor, gate_offset: int, eps: float, out: torch.Tensor, *,

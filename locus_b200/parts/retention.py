@@ -67,8 +67,11 @@ class Retention(Mixer):
             # a call that reads another call's state must leave it as it found it
             state = rt.buf("retention.state_copy", tuple(cache.state.shape), torch.float32)
             state.copy_(cache.state)
+        qn = batch.host_seg_qn
+        short = not qn or min(qn) < K.RETENTION_CHUNK_FROM
+        long = not qn or max(qn) >= K.RETENTION_CHUNK_FROM
         K.retention_scan(qkvg, state, batch.state_slots, batch.seg_q0, batch.seg_qn, batch.n_seg, self._decay,
-                         self.d ** -0.5, o_raw, n_heads=self.H, dim=self.d, v_dim=self.dv)
+                         self.d ** -0.5, o_raw, n_heads=self.H, dim=self.d, v_dim=self.dv, short=short, long=long)
         o = rt.rows("retention.o", self.H * self.dv, rt.dtype, T)
         K.retention_gate_norm(o_raw, qkvg, 2 * self.H * self.d + self.H * self.dv, self.eps, o, n_heads=self.H,
                               v_dim=self.dv)

@@ -430,7 +430,8 @@ def heads_to_rows(src_hm, out, *, n_tokens, n_heads):
     out[:n_tokens] = src_hm[: n_heads * n_tokens].view(n_heads, n_tokens, d).transpose(0, 1).reshape(n_tokens, n_heads * d)
 
 
-def retention_scan(qkvg, state, state_slots, seg_q0, seg_qn, n_seg, decay, k_scale, o_raw, *, n_heads, dim, v_dim):
+def retention_scan(qkvg, state, state_slots, seg_q0, seg_qn, n_seg, decay, k_scale, o_raw, *, n_heads, dim, v_dim,
+                   short=True, long=True):
     H, d, dv = n_heads, dim, v_dim
     for seg in range(n_seg):
         q0, qn, slot = int(seg_q0[seg]), int(seg_qn[seg]), int(state_slots[seg])

@@ -152,7 +152,8 @@ class Case:
     def ref_following(self, rid, routed, near_tie):
         """The oracle's logits when it takes the engine's picks (``routed``: prefix -> {position: picks}) where they
         differ from its own.  A difference is allowed only at a near-tie: every expert the engine picked must have
-        a logit within ``near_tie`` (absolute) of the oracle's weakest own pick."""
+        a logit within ``near_tie`` times the spread of the token's logits (largest minus smallest) of the oracle's
+        weakest own pick."""
         base, aux = self.ref(rid)
         T = len(self.tokens[rid])
         forced, differs = {}, 0
@@ -167,8 +168,9 @@ class Case:
                 if sorted(eng) != sorted(mine):
                     differs += 1
                     weakest = min(float(z[pos, e]) for e in mine)
+                    spread = float(z[pos].max() - z[pos].min())
                     for e in eng:
-                        assert float(z[pos, e]) >= weakest - near_tie, (
+                        assert float(z[pos, e]) >= weakest - near_tie * spread, (
                             f"{self.name}/{rid} {prefix} position {pos}: the engine picked expert {e} with logit "
                             f"{float(z[pos, e]):.5f}; the oracle's weakest pick has {weakest:.5f}")
                 rows.append(eng)

@@ -22,7 +22,7 @@ ROOT = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
 
 # max and mean |error| of the logits (their mean over the vocabulary taken off) relative to the largest |logit|
 TOL = {torch.float32: (5e-5, 1e-5), torch.bfloat16: (3e-2, 5e-3)}
-NEAR_TIE = {torch.float32: 1e-4, torch.bfloat16: 5e-2}   # absolute, in router logits (they spread over several units)
+NEAR_TIE = {torch.float32: 2e-5, torch.bfloat16: 2e-2}   # of the spread of a token's router logits
 DTYPES = [torch.float32, torch.bfloat16]
 LENGTHS = {"mix": (1, 2, 37, 70, 45, 19, 130), "odd": (3, 90, 33, 16, 75), "wide": (150, 40, 260),
            "latent_only": (50, 23), "latent_full": (80,), "retention_only": (70, 5), "dense_only": (20,),
@@ -219,7 +219,9 @@ def test_retention_kernels_against_their_twins(heads, dim, v_dim):
     q0b = torch.tensor([a + f for a, f in zip([0, 19, 20, 60], first)], dtype=torch.int32).cuda()
     K.retention_scan(qkvg, state2, slots, q0b, torch.tensor([n - f for n, f in zip(segs, first)], dtype=torch.int32).cuda(),
                      4, decay, dim ** -0.5, o2, n_heads=heads, dim=dim, v_dim=v_dim)
-    assert torch.equal(o2, o_raw) and torch.equal(state2, state)
+    # (a half may be short enough for the token-by-token kernel where the whole went chunk by chunk: rounding only)
+    assert float((o2 - o_raw).abs().max()) <= 2e-5 * float(o_raw.abs().max())
+    assert float((state2 - state).abs().max()) <= 2e-5 * float(state.abs().max())
     for odt in DTYPES:
         out = torch.zeros(T, heads * v_dim, dtype=odt, device="cuda")
         K.retention_gate_norm(o_raw, qkvg, 2 * heads * dim + heads * v_dim, 1e-5, out, n_heads=heads, v_dim=v_dim)

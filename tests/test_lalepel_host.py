@@ -17,7 +17,7 @@ from locus_b200.config import ConfigError, find_arch
 from locus_b200.config.lalepel import LalepelConfig
 
 TOL = (2e-5, 4e-6)   # max and mean |error| of the logits relative to the largest |logit|; float32 twins
-NEAR_TIE = 1e-4
+NEAR_TIE = 2e-5
 
 
 @pytest.fixture(autouse=True)
