@@ -136,7 +136,7 @@ __global__ void __launch_bounds__(256) retention_chunked_kernel(
     const float* __restrict__ qkvg, int ld, float* __restrict__ state, const int* __restrict__ state_slots,
     const int* __restrict__ seg_q0, const int* __restrict__ seg_qn, const float* __restrict__ decay, float k_scale,
     float* __restrict__ o_raw, int H, int d, int dv, int col_groups, int qn_from) {
-    extern __shared__ float rc_smem[];
+    extern __shared__ __align__(16) float rc_smem[];
     pdl_entry();
     pdl_trigger();
     const int seg = blockIdx.y;
@@ -144,19 +144,21 @@ __global__ void __launch_bounds__(256) retention_chunked_kernel(
     if (qn < qn_from) return;  // a short portion or a single token: the scan kernel's
     const int h = blockIdx.x / col_groups, c0 = (blockIdx.x % col_groups) * RC_COLS;
     const int q0 = seg_q0[seg];
-    const int ldq = d + 1;
-    float* Qs = rc_smem;                      // [C][d + 1]
-    float* Ks = Qs + RC_CHUNK * ldq;          // [C][d + 1]
+    // Rows of Q, K and A are read four elements at a time (16-byte rows, padded by one 16-byte piece so that the lanes of
+    // a warp that read different rows hit different banks); d4 = d rounded up to a multiple of 4, the tail zero.
+    const int d4 = (d + 3) & ~3, ldq = d4 + 4, lda = RC_CHUNK + 4;
+    float* Qs = rc_smem;                      // [C][ldq]
+    float* Ks = Qs + RC_CHUNK * ldq;          // [C][ldq]
     float* Vs = Ks + RC_CHUNK * ldq;          // [C][RC_COLS]
-    float* As = Vs + RC_CHUNK * RC_COLS;      // [C][C + 1]
-    float* Ss = As + RC_CHUNK * (RC_CHUNK + 1);  // [d][RC_COLS]
-    float* pw = Ss + d * RC_COLS;             // [C + 1] powers of the decay
+    float* As = Vs + RC_CHUNK * RC_COLS;      // [C][lda]
+    float* Ss = As + RC_CHUNK * lda;          // [d4][RC_COLS]
+    float* pw = Ss + d4 * RC_COLS;            // [C + 1] powers of the decay
     const int tid = threadIdx.x, lane = tid & 31, wid = tid >> 5;
     const float lam = decay[h];
     float* S = state + (static_cast<size_t>(state_slots[seg]) * H + h) * d * dv;
-    for (int i = tid; i < d * RC_COLS; i += 256) {
+    for (int i = tid; i < d4 * RC_COLS; i += 256) {
         const int r = i / RC_COLS, c = i % RC_COLS;
-        Ss[i] = c0 + c < dv ? S[static_cast<size_t>(r) * dv + c0 + c] : 0.f;
+        Ss[i] = (r < d && c0 + c < dv) ? S[static_cast<size_t>(r) * dv + c0 + c] : 0.f;
     }
     if (tid == 0) {
         float p = 1.f;
@@ -166,53 +168,92 @@ __global__ void __launch_bounds__(256) retention_chunked_kernel(
         }
     }
     const int off_q = h * d, off_k = H * d + h * d, off_v = 2 * H * d + h * dv + c0;
+    const int rows_w = (d4 / 4 + 7) / 8 * 4;  // state rows of a warp in the update (a multiple of 4)
     for (int t0 = 0; t0 < qn; t0 += RC_CHUNK) {
         const int n = min(RC_CHUNK, qn - t0);
         __syncthreads();  // the state and the last chunk's operands are free
-        for (int i = tid; i < RC_CHUNK * d; i += 256) {
-            const int j = i / d, r = i % d;
+        for (int i = tid; i < RC_CHUNK * d4; i += 256) {
+            const int j = i / d4, r = i % d4;
             const float* row = qkvg + static_cast<size_t>(q0 + t0 + j) * ld;
-            Qs[j * ldq + r] = j < n ? row[off_q + r] : 0.f;
-            Ks[j * ldq + r] = j < n ? row[off_k + r] * k_scale : 0.f;
+            const bool ok = j < n && r < d;
+            Qs[j * ldq + r] = ok ? row[off_q + r] : 0.f;
+            Ks[j * ldq + r] = ok ? row[off_k + r] * k_scale : 0.f;
         }
         for (int i = tid; i < RC_CHUNK * RC_COLS; i += 256) {
             const int j = i / RC_COLS, c = i % RC_COLS;
             Vs[i] = (j < n && c0 + c < dv) ? qkvg[static_cast<size_t>(q0 + t0 + j) * ld + off_v + c] : 0.f;
         }
         __syncthreads();
-        // A = (Q K^T) * D: row i = wid + 8 u, column j = lane
+        // A = (Q K^T) * D: rows i = wid + 8 u, column j = lane
+        {
+            float acc[4] = {0.f, 0.f, 0.f, 0.f};
+            const float4* kr = reinterpret_cast<const float4*>(Ks + lane * ldq);
+            for (int r4 = 0; r4 < d4 / 4; ++r4) {
+                const float4 k = kr[r4];
 #pragma unroll
-        for (int u = 0; u < RC_CHUNK / 8; ++u) {
-            const int i = wid + 8 * u, j = lane;
-            float dot = 0.f;
-            if (j <= i) {
-                const float* qr = Qs + i * ldq;
-                const float* kr = Ks + j * ldq;
-                for (int r = 0; r < d; ++r) dot = fmaf(qr[r], kr[r], dot);
-                dot *= pw[i - j];
+                for (int u = 0; u < 4; ++u) {
+                    const float4 q = reinterpret_cast<const float4*>(Qs + (wid + 8 * u) * ldq)[r4];
+                    acc[u] = fmaf(q.x, k.x, acc[u]);
+                    acc[u] = fmaf(q.y, k.y, acc[u]);
+                    acc[u] = fmaf(q.z, k.z, acc[u]);
+                    acc[u] = fmaf(q.w, k.w, acc[u]);
+                }
             }
-            As[i * (RC_CHUNK + 1) + j] = dot;
-        }
-        __syncthreads();
-        // O = A V + decay^(i+1) Q S: row i = wid + 8 u, column c = lane
 #pragma unroll
-        for (int u = 0; u < RC_CHUNK / 8; ++u) {
-            const int i = wid + 8 * u;
-            if (i >= n) continue;
-            float intra = 0.f, inter = 0.f;
-            const float* ar = As + i * (RC_CHUNK + 1);
-            for (int j = 0; j <= i; ++j) intra = fmaf(ar[j], Vs[j * RC_COLS + lane], intra);
-            const float* qr = Qs + i * ldq;
-            for (int r = 0; r < d; ++r) inter = fmaf(qr[r], Ss[r * RC_COLS + lane], inter);
-            if (c0 + lane < dv)
-                o_raw[static_cast<size_t>(q0 + t0 + i) * H * dv + h * dv + c0 + lane] = fmaf(pw[i + 1], inter, intra);
+            for (int u = 0; u < 4; ++u) {
+                const int i = wid + 8 * u;
+                As[i * lda + lane] = lane <= i ? acc[u] * pw[i - lane] : 0.f;
+            }
         }
         __syncthreads();
-        // S <- decay^n S + (K * decay^(n-1-j))^T V: row r = wid + 8 u, column c = lane
-        for (int r = wid; r < d; r += 8) {
-            float acc = 0.f;
-            for (int j = 0; j < n; ++j) acc = fmaf(Ks[j * ldq + r] * pw[n - 1 - j], Vs[j * RC_COLS + lane], acc);
-            Ss[r * RC_COLS + lane] = fmaf(pw[n], Ss[r * RC_COLS + lane], acc);
+        // O = A V + decay^(i+1) Q S: rows i = wid + 8 u, column c = lane
+        {
+            float intra[4] = {0.f, 0.f, 0.f, 0.f}, inter[4] = {0.f, 0.f, 0.f, 0.f};
+            for (int j4 = 0; j4 < RC_CHUNK / 4; ++j4) {
+                const float v0 = Vs[(4 * j4) * RC_COLS + lane], v1 = Vs[(4 * j4 + 1) * RC_COLS + lane];
+                const float v2 = Vs[(4 * j4 + 2) * RC_COLS + lane], v3 = Vs[(4 * j4 + 3) * RC_COLS + lane];
+#pragma unroll
+                for (int u = 0; u < 4; ++u) {
+                    const float4 p = reinterpret_cast<const float4*>(As + (wid + 8 * u) * lda)[j4];
+                    intra[u] = fmaf(p.x, v0, intra[u]);
+                    intra[u] = fmaf(p.y, v1, intra[u]);
+                    intra[u] = fmaf(p.z, v2, intra[u]);
+                    intra[u] = fmaf(p.w, v3, intra[u]);
+                }
+            }
+            for (int r4 = 0; r4 < d4 / 4; ++r4) {
+                const float s0 = Ss[(4 * r4) * RC_COLS + lane], s1 = Ss[(4 * r4 + 1) * RC_COLS + lane];
+                const float s2 = Ss[(4 * r4 + 2) * RC_COLS + lane], s3 = Ss[(4 * r4 + 3) * RC_COLS + lane];
+#pragma unroll
+                for (int u = 0; u < 4; ++u) {
+                    const float4 q = reinterpret_cast<const float4*>(Qs + (wid + 8 * u) * ldq)[r4];
+                    inter[u] = fmaf(q.x, s0, inter[u]);
+                    inter[u] = fmaf(q.y, s1, inter[u]);
+                    inter[u] = fmaf(q.z, s2, inter[u]);
+                    inter[u] = fmaf(q.w, s3, inter[u]);
+                }
+            }
+#pragma unroll
+            for (int u = 0; u < 4; ++u) {
+                const int i = wid + 8 * u;
+                if (i < n && c0 + lane < dv)
+                    o_raw[static_cast<size_t>(q0 + t0 + i) * H * dv + h * dv + c0 + lane] = fmaf(pw[i + 1], inter[u], intra[u]);
+            }
+        }
+        __syncthreads();
+        // S <- decay^n S + (K * decay^(n-1-j))^T V: rows wid * rows_w .., column c = lane
+        for (int r0 = wid * rows_w; r0 < min(d4, (wid + 1) * rows_w); r0 += 4) {
+            float acc[4] = {0.f, 0.f, 0.f, 0.f};
+            for (int j = 0; j < n; ++j) {
+                const float v = Vs[j * RC_COLS + lane] * pw[n - 1 - j];
+                const float4 k = *reinterpret_cast<const float4*>(Ks + j * ldq + r0);
+                acc[0] = fmaf(k.x, v, acc[0]);
+                acc[1] = fmaf(k.y, v, acc[1]);
+                acc[2] = fmaf(k.z, v, acc[2]);
+                acc[3] = fmaf(k.w, v, acc[3]);
+            }
+#pragma unroll
+            for (int e = 0; e < 4; ++e) Ss[(r0 + e) * RC_COLS + lane] = fmaf(pw[n], Ss[(r0 + e) * RC_COLS + lane], acc[e]);
         }
     }
     __syncthreads();
@@ -231,8 +272,9 @@ extern "C" int locus_retention_chunked(const float* qkvg, int ld, float* state, 
     if (H <= 0 || d <= 0 || d > 256 || dv <= 0 || n_seg > 65535 || ld < 2 * H * d + 2 * H * dv || qn_from < 1)
         return LOCUS_ERR_UNSUPPORTED;
     const int col_groups = (dv + RC_COLS - 1) / RC_COLS;
-    const size_t smem = sizeof(float) * (2 * RC_CHUNK * (d + 1) + RC_CHUNK * RC_COLS + RC_CHUNK * (RC_CHUNK + 1) +
-                                         static_cast<size_t>(d) * RC_COLS + RC_CHUNK + 1);
+    const int d4 = (d + 3) & ~3;
+    const size_t smem = sizeof(float) * (2 * RC_CHUNK * (d4 + 4) + RC_CHUNK * RC_COLS + RC_CHUNK * (RC_CHUNK + 4) +
+                                         static_cast<size_t>(d4) * RC_COLS + RC_CHUNK + 4);
     if (smem > 48 * 1024 &&
         cudaFuncSetAttribute(retention_chunked_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize,
                              static_cast<int>(smem)) != cudaSuccess)

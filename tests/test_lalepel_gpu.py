@@ -22,7 +22,8 @@ ROOT = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
 
 # max and mean |error| of the logits (their mean over the vocabulary taken off) relative to the largest |logit|
 TOL = {torch.float32: (5e-5, 1e-5), torch.bfloat16: (3e-2, 5e-3)}
-NEAR_TIE = {torch.float32: 2e-5, torch.bfloat16: 2e-2}   # of the spread of a token's router logits
+NEAR_TIE = {torch.float32: 2e-5, torch.bfloat16: 5e-2}   # of the spread of a token's router logits (measured: rounding the
+# sublayers' inputs alone moves a logit by up to 1.5 % of the spread at width 128)
 DTYPES = [torch.float32, torch.bfloat16]
 LENGTHS = {"mix": (1, 2, 37, 70, 45, 19, 130), "odd": (3, 90, 33, 16, 75), "wide": (150, 40, 260),
            "latent_only": (50, 23), "latent_full": (80,), "retention_only": (70, 5), "dense_only": (20,),
@@ -308,3 +309,25 @@ def test_trace_replay_as_a_program(cases, tmp_path):
             # a near-tie of the router may go either way here; such rows are judged in the schedule tests above
             if float((d - d.mean()).abs().max()) > tol * float(ref.abs().max()) and dtype == "float32":
                 raise AssertionError(f"step {n} {rid} position {pos}: off by {float((d - d.mean()).abs().max()):.2e}")
+
+
+def test_the_command_line_generates_from_a_folder_of_this_design(cases):
+    """bin/locus-run: the architecture is found by config.json, the weights by name, and greedy generation gives the
+    oracle's tokens (where its two best logits are not a near-tie)."""
+    case = cases("no_router")
+    prompt = case.tokens["r0"][:12]
+    p = subprocess.run([sys.executable, os.path.join(ROOT, "bin", "locus-run"), case.dir, ",".join(map(str, prompt)), "8",
+                        "--dtype", "float32", "--page-tokens", "16", "--ctx", "128"], capture_output=True, text=True,
+                       timeout=900)
+    assert p.returncode == 0, p.stderr[-2000:]
+    out = [int(x) for x in p.stdout.replace(",", " ").split() if x.lstrip("-").isdigit()]
+    assert len(out) >= 8
+    seq = list(prompt)
+    for tok in out[-8:]:
+        lg, _ = plain.forward(case.cfg, case.weights, seq)
+        top2 = torch.topk(lg[-1], 2).values
+        if float(top2[0] - top2[1]) > 1e-3 * float(lg[-1].abs().max()):
+            assert int(torch.argmax(lg[-1])) == tok
+        seq.append(tok)
+    archs = subprocess.run([sys.executable, os.path.join(ROOT, "bin", "locus-run"), "--archs"], capture_output=True, text=True)
+    assert "Lalepel" in archs.stdout
