@@ -63,6 +63,11 @@ CONFIGS = {
         with_mlp(latent(1, 12, 6, 10, 20, 28, window=1, scaling={"factor": 2.0, "original": 32, "fast": 8.0, "slow": 1.0}), DENSE(36)),
         with_mlp(latent(5, 4, 2, 6, 12, 12, window=70), None),
     ], eps=1e-6),
+    # nothing a multiple of 4: width 50, a latent of 10 + 4, rows of 5 and 3
+    "odd2": model(50, 33, [
+        with_mlp(latent(2, 6, 4, 5, 9, 10, window=5), MOE(3, 2, 7, shared=5)),
+        with_mlp(retention(1, 5, 3, [0.8]), DENSE(9)),
+    ]),
     # one layer each: a mechanism alone
     "latent_only": model(48, 50, [with_mlp(latent(4, 8, 16, 8, 16, 32, window=20, scaling=SCALING), None)]),
     "latent_full": model(48, 50, [with_mlp(latent(2, 16, 0, 8, 32, 40, rot_dims=0), None)]),

@@ -27,7 +27,7 @@ NEAR_TIE = {torch.float32: 2e-5, torch.bfloat16: 5e-2}   # of the spread of a to
 DTYPES = [torch.float32, torch.bfloat16]
 LENGTHS = {"mix": (1, 2, 37, 70, 45, 19, 130), "odd": (3, 90, 33, 16, 75), "wide": (150, 40, 260),
            "latent_only": (50, 23), "latent_full": (80,), "retention_only": (70, 5), "dense_only": (20,),
-           "moe_only": (40,), "no_router": (30,)}
+           "moe_only": (40,), "no_router": (30,), "odd2": (44, 3, 21)}
 
 
 @pytest.fixture(scope="module")

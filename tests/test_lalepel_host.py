@@ -87,7 +87,7 @@ def test_plain_retention_is_the_decayed_sum():
 
 @pytest.mark.parametrize("name,lengths", [("mix", (1, 2, 37, 70, 45, 19)), ("odd", (3, 90, 33, 16, 75)),
                                           ("latent_only", (50,)), ("latent_full", (40,)), ("retention_only", (50,)),
-                                          ("dense_only", (20,)), ("moe_only", (30,))])
+                                          ("dense_only", (20,)), ("moe_only", (30,)), ("odd2", (44, 3, 21))])
 def test_every_schedule_agrees_with_plain(name, lengths, tmp_path):
     case = Case(name, tmp_path, torch.float32, requests=lengths)
     runner, cache = make_runner(case, torch.float32, "cpu", page_tokens=8, n_pages=30, max_tokens=128)
