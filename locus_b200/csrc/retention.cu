@@ -13,8 +13,8 @@
 //                        (up to 8 rows: d <= 256); per token one butterfly sum per column.  The order of every
 //                        sum is fixed by d alone, so a token's output does not depend on how the request's
 //                        tokens were cut into steps or on what else the step holds.
-//   retention_chunked    the same recurrence for long portions, a chunk of 32 tokens at a time as small matrix
-//                        products (see there)
+//   retention_intra /    the same recurrence for long portions, a chunk of 32 tokens at a time as small matrix
+//   retention_inter      products (see there)
 //   retention_gate_norm  out[t, h, :] = o[t, h, :] / rms(o[t, h, :]) * silu(g[t, h, :])   (a warp per row and head)
 #include "common.cuh"
 
@@ -127,38 +127,123 @@ extern "C" int locus_retention_scan(const float* qkvg, int ld, float* state, con
 //     S <- decay^n S + (K * decay^(n-1-j))^T V          (n: the chunk's tokens)
 //
 // which is the recurrence above summed in another order (float32 FMAs on the CUDA cores; the powers of the decay by
-// repeated multiplication).  A block owns RC_COLS columns of one head's state for one request, keeps them in shared
-// memory across the request's chunks, and only the state couples a chunk to the next.
+// repeated multiplication).  Two kernels.  The first term needs no state: retention_intra_kernel forms it for every
+// (request, chunk, head) at once and writes it to o_raw.  retention_inter_kernel then walks a request's chunks in
+// order: a block owns `cols` (8, 16 or 32: as many as it takes to fill the GPU) columns of one head's state, keeps them
+// in shared memory across the chunks, adds the second term to o_raw and moves the state on.  Rows of Q, K and A are
+// read four elements at a time (16-byte rows, padded by one 16-byte piece so that lanes that read different rows hit
+// different banks); d4 = d rounded up to a multiple of 4, the tail zero.
 #define RC_CHUNK 32
-#define RC_COLS 32
 
-__global__ void __launch_bounds__(256) retention_chunked_kernel(
+__global__ void __launch_bounds__(256) retention_intra_kernel(
+    const float* __restrict__ qkvg, int ld, const int* __restrict__ seg_q0, const int* __restrict__ seg_qn,
+    const float* __restrict__ decay, float k_scale, float* __restrict__ o_raw, int H, int d, int dv, int qn_from) {
+    extern __shared__ __align__(16) float rc_smem[];
+    __shared__ float pw[RC_CHUNK + 1];
+    pdl_entry();
+    pdl_trigger();
+    const int seg = blockIdx.z, h = blockIdx.y;
+    const int qn = seg_qn[seg], t0 = blockIdx.x * RC_CHUNK;
+    if (qn < qn_from || t0 >= qn) return;
+    const int n = min(RC_CHUNK, qn - t0), q0 = seg_q0[seg];
+    const int d4 = (d + 3) & ~3, ldq = d4 + 4, lda = RC_CHUNK + 4, dvp = (dv + 31) & ~31;
+    float* Qs = rc_smem;                      // [C][ldq]
+    float* Ks = Qs + RC_CHUNK * ldq;          // [C][ldq]
+    float* As = Ks + RC_CHUNK * ldq;          // [C][lda]
+    float* Vs = As + RC_CHUNK * lda;          // [C][dvp]
+    const int tid = threadIdx.x, lane = tid & 31, wid = tid >> 5;
+    if (tid == 0) {
+        float p = 1.f;
+        const float lam = decay[h];
+        for (int i = 0; i <= RC_CHUNK; ++i) {
+            pw[i] = p;
+            p *= lam;
+        }
+    }
+    const int off_q = h * d, off_k = H * d + h * d, off_v = 2 * H * d + h * dv;
+    for (int i = tid; i < RC_CHUNK * d4; i += 256) {
+        const int j = i / d4, r = i % d4;
+        const float* row = qkvg + static_cast<size_t>(q0 + t0 + j) * ld;
+        const bool ok = j < n && r < d;
+        Qs[j * ldq + r] = ok ? row[off_q + r] : 0.f;
+        Ks[j * ldq + r] = ok ? row[off_k + r] * k_scale : 0.f;
+    }
+    for (int i = tid; i < RC_CHUNK * dvp; i += 256) {
+        const int j = i / dvp, c = i % dvp;
+        Vs[i] = (j < n && c < dv) ? qkvg[static_cast<size_t>(q0 + t0 + j) * ld + off_v + c] : 0.f;
+    }
+    __syncthreads();
+    {   // A = (Q K^T) * D: rows i = wid + 8 u, column j = lane
+        float acc[4] = {0.f, 0.f, 0.f, 0.f};
+        const float4* kr = reinterpret_cast<const float4*>(Ks + lane * ldq);
+        for (int r4 = 0; r4 < d4 / 4; ++r4) {
+            const float4 k = kr[r4];
+#pragma unroll
+            for (int u = 0; u < 4; ++u) {
+                const float4 q = reinterpret_cast<const float4*>(Qs + (wid + 8 * u) * ldq)[r4];
+                acc[u] = fmaf(q.x, k.x, acc[u]);
+                acc[u] = fmaf(q.y, k.y, acc[u]);
+                acc[u] = fmaf(q.z, k.z, acc[u]);
+                acc[u] = fmaf(q.w, k.w, acc[u]);
+            }
+        }
+#pragma unroll
+        for (int u = 0; u < 4; ++u) {
+            const int i = wid + 8 * u;
+            As[i * lda + lane] = lane <= i ? acc[u] * pw[i - lane] : 0.f;
+        }
+    }
+    __syncthreads();
+    // A V: rows i = wid + 8 u, columns lane + 32 cc
+    for (int cc = 0; cc < dvp / 32; ++cc) {
+        const int c = lane + 32 * cc;
+        float intra[4] = {0.f, 0.f, 0.f, 0.f};
+        for (int j4 = 0; j4 < RC_CHUNK / 4; ++j4) {
+            const float v0 = Vs[(4 * j4) * dvp + c], v1 = Vs[(4 * j4 + 1) * dvp + c];
+            const float v2 = Vs[(4 * j4 + 2) * dvp + c], v3 = Vs[(4 * j4 + 3) * dvp + c];
+#pragma unroll
+            for (int u = 0; u < 4; ++u) {
+                const float4 p = reinterpret_cast<const float4*>(As + (wid + 8 * u) * lda)[j4];
+                intra[u] = fmaf(p.x, v0, intra[u]);
+                intra[u] = fmaf(p.y, v1, intra[u]);
+                intra[u] = fmaf(p.z, v2, intra[u]);
+                intra[u] = fmaf(p.w, v3, intra[u]);
+            }
+        }
+#pragma unroll
+        for (int u = 0; u < 4; ++u) {
+            const int i = wid + 8 * u;
+            if (i < n && c < dv) o_raw[static_cast<size_t>(q0 + t0 + i) * H * dv + h * dv + c] = intra[u];
+        }
+    }
+}
+
+__global__ void __launch_bounds__(256) retention_inter_kernel(
     const float* __restrict__ qkvg, int ld, float* __restrict__ state, const int* __restrict__ state_slots,
     const int* __restrict__ seg_q0, const int* __restrict__ seg_qn, const float* __restrict__ decay, float k_scale,
-    float* __restrict__ o_raw, int H, int d, int dv, int col_groups, int qn_from) {
+    float* __restrict__ o_raw, int H, int d, int dv, int col_groups, int cols, int qn_from) {
     extern __shared__ __align__(16) float rc_smem[];
     pdl_entry();
     pdl_trigger();
     const int seg = blockIdx.y;
     const int qn = seg_qn[seg];
     if (qn < qn_from) return;  // a short portion or a single token: the scan kernel's
-    const int h = blockIdx.x / col_groups, c0 = (blockIdx.x % col_groups) * RC_COLS;
+    const int h = blockIdx.x / col_groups, c0 = (blockIdx.x % col_groups) * cols;
     const int q0 = seg_q0[seg];
-    // Rows of Q, K and A are read four elements at a time (16-byte rows, padded by one 16-byte piece so that the lanes of
-    // a warp that read different rows hit different banks); d4 = d rounded up to a multiple of 4, the tail zero.
-    const int d4 = (d + 3) & ~3, ldq = d4 + 4, lda = RC_CHUNK + 4;
+    const int d4 = (d + 3) & ~3, ldq = d4 + 4;
     float* Qs = rc_smem;                      // [C][ldq]
     float* Ks = Qs + RC_CHUNK * ldq;          // [C][ldq]
-    float* Vs = Ks + RC_CHUNK * ldq;          // [C][RC_COLS]
-    float* As = Vs + RC_CHUNK * RC_COLS;      // [C][lda]
-    float* Ss = As + RC_CHUNK * lda;          // [d4][RC_COLS]
-    float* pw = Ss + d4 * RC_COLS;            // [C + 1] powers of the decay
+    float* Vs = Ks + RC_CHUNK * ldq;          // [C][cols]
+    float* Ss = Vs + RC_CHUNK * cols;         // [d4][cols]
+    float* pw = Ss + d4 * cols;               // [C + 1] powers of the decay
     const int tid = threadIdx.x, lane = tid & 31, wid = tid >> 5;
+    // a warp's lanes: `cols` columns times 32 / cols shares of the rows
+    const int c = lane % cols, sub = lane / cols, nsub = 32 / cols;
     const float lam = decay[h];
     float* S = state + (static_cast<size_t>(state_slots[seg]) * H + h) * d * dv;
-    for (int i = tid; i < d4 * RC_COLS; i += 256) {
-        const int r = i / RC_COLS, c = i % RC_COLS;
-        Ss[i] = (r < d && c0 + c < dv) ? S[static_cast<size_t>(r) * dv + c0 + c] : 0.f;
+    for (int i = tid; i < d4 * cols; i += 256) {
+        const int r = i / cols, cc = i % cols;
+        Ss[i] = (r < d && c0 + cc < dv) ? S[static_cast<size_t>(r) * dv + c0 + cc] : 0.f;
     }
     if (tid == 0) {
         float p = 1.f;
@@ -168,7 +253,9 @@ __global__ void __launch_bounds__(256) retention_chunked_kernel(
         }
     }
     const int off_q = h * d, off_k = H * d + h * d, off_v = 2 * H * d + h * dv + c0;
-    const int rows_w = (d4 / 4 + 7) / 8 * 4;  // state rows of a warp in the update (a multiple of 4)
+    const int owners = 8 * nsub;                                   // (warp, share) pairs that split the state's rows
+    const int rows_o = ((d4 / 4 + owners - 1) / owners) * 4;       // rows of one of them (a multiple of 4)
+    const int r_lo = (wid * nsub + sub) * rows_o, r_hi = min(d4, r_lo + rows_o);
     for (int t0 = 0; t0 < qn; t0 += RC_CHUNK) {
         const int n = min(RC_CHUNK, qn - t0);
         __syncthreads();  // the state and the last chunk's operands are free
@@ -179,51 +266,16 @@ __global__ void __launch_bounds__(256) retention_chunked_kernel(
             Qs[j * ldq + r] = ok ? row[off_q + r] : 0.f;
             Ks[j * ldq + r] = ok ? row[off_k + r] * k_scale : 0.f;
         }
-        for (int i = tid; i < RC_CHUNK * RC_COLS; i += 256) {
-            const int j = i / RC_COLS, c = i % RC_COLS;
-            Vs[i] = (j < n && c0 + c < dv) ? qkvg[static_cast<size_t>(q0 + t0 + j) * ld + off_v + c] : 0.f;
+        for (int i = tid; i < RC_CHUNK * cols; i += 256) {
+            const int j = i / cols, cc = i % cols;
+            Vs[i] = (j < n && c0 + cc < dv) ? qkvg[static_cast<size_t>(q0 + t0 + j) * ld + off_v + cc] : 0.f;
         }
         __syncthreads();
-        // A = (Q K^T) * D: rows i = wid + 8 u, column j = lane
-        {
-            float acc[4] = {0.f, 0.f, 0.f, 0.f};
-            const float4* kr = reinterpret_cast<const float4*>(Ks + lane * ldq);
-            for (int r4 = 0; r4 < d4 / 4; ++r4) {
-                const float4 k = kr[r4];
-#pragma unroll
-                for (int u = 0; u < 4; ++u) {
-                    const float4 q = reinterpret_cast<const float4*>(Qs + (wid + 8 * u) * ldq)[r4];
-                    acc[u] = fmaf(q.x, k.x, acc[u]);
-                    acc[u] = fmaf(q.y, k.y, acc[u]);
-                    acc[u] = fmaf(q.z, k.z, acc[u]);
-                    acc[u] = fmaf(q.w, k.w, acc[u]);
-                }
-            }
-#pragma unroll
-            for (int u = 0; u < 4; ++u) {
-                const int i = wid + 8 * u;
-                As[i * lda + lane] = lane <= i ? acc[u] * pw[i - lane] : 0.f;
-            }
-        }
-        __syncthreads();
-        // O = A V + decay^(i+1) Q S: rows i = wid + 8 u, column c = lane
-        {
-            float intra[4] = {0.f, 0.f, 0.f, 0.f}, inter[4] = {0.f, 0.f, 0.f, 0.f};
-            for (int j4 = 0; j4 < RC_CHUNK / 4; ++j4) {
-                const float v0 = Vs[(4 * j4) * RC_COLS + lane], v1 = Vs[(4 * j4 + 1) * RC_COLS + lane];
-                const float v2 = Vs[(4 * j4 + 2) * RC_COLS + lane], v3 = Vs[(4 * j4 + 3) * RC_COLS + lane];
-#pragma unroll
-                for (int u = 0; u < 4; ++u) {
-                    const float4 p = reinterpret_cast<const float4*>(As + (wid + 8 * u) * lda)[j4];
-                    intra[u] = fmaf(p.x, v0, intra[u]);
-                    intra[u] = fmaf(p.y, v1, intra[u]);
-                    intra[u] = fmaf(p.z, v2, intra[u]);
-                    intra[u] = fmaf(p.w, v3, intra[u]);
-                }
-            }
-            for (int r4 = 0; r4 < d4 / 4; ++r4) {
-                const float s0 = Ss[(4 * r4) * RC_COLS + lane], s1 = Ss[(4 * r4 + 1) * RC_COLS + lane];
-                const float s2 = Ss[(4 * r4 + 2) * RC_COLS + lane], s3 = Ss[(4 * r4 + 3) * RC_COLS + lane];
+        {   // o += decay^(i+1) Q S: rows i = wid + 8 u, column c; the lanes' shares of the rows of S are summed by shuffles
+            float inter[4] = {0.f, 0.f, 0.f, 0.f};
+            for (int r4 = sub; r4 < d4 / 4; r4 += nsub) {
+                const float s0 = Ss[(4 * r4) * cols + c], s1 = Ss[(4 * r4 + 1) * cols + c];
+                const float s2 = Ss[(4 * r4 + 2) * cols + c], s3 = Ss[(4 * r4 + 3) * cols + c];
 #pragma unroll
                 for (int u = 0; u < 4; ++u) {
                     const float4 q = reinterpret_cast<const float4*>(Qs + (wid + 8 * u) * ldq)[r4];
@@ -235,17 +287,20 @@ __global__ void __launch_bounds__(256) retention_chunked_kernel(
             }
 #pragma unroll
             for (int u = 0; u < 4; ++u) {
+                for (int o = cols; o < 32; o <<= 1) inter[u] += __shfl_xor_sync(0xffffffffu, inter[u], o);
                 const int i = wid + 8 * u;
-                if (i < n && c0 + lane < dv)
-                    o_raw[static_cast<size_t>(q0 + t0 + i) * H * dv + h * dv + c0 + lane] = fmaf(pw[i + 1], inter[u], intra[u]);
+                if (sub == 0 && i < n && c0 + c < dv) {
+                    float* dst = o_raw + static_cast<size_t>(q0 + t0 + i) * H * dv + h * dv + c0 + c;
+                    *dst = fmaf(pw[i + 1], inter[u], *dst);
+                }
             }
         }
         __syncthreads();
-        // S <- decay^n S + (K * decay^(n-1-j))^T V: rows wid * rows_w .., column c = lane
-        for (int r0 = wid * rows_w; r0 < min(d4, (wid + 1) * rows_w); r0 += 4) {
+        // S <- decay^n S + (K * decay^(n-1-j))^T V: this lane's rows, column c
+        for (int r0 = r_lo; r0 < r_hi; r0 += 4) {
             float acc[4] = {0.f, 0.f, 0.f, 0.f};
             for (int j = 0; j < n; ++j) {
-                const float v = Vs[j * RC_COLS + lane] * pw[n - 1 - j];
+                const float v = Vs[j * cols + c] * pw[n - 1 - j];
                 const float4 k = *reinterpret_cast<const float4*>(Ks + j * ldq + r0);
                 acc[0] = fmaf(k.x, v, acc[0]);
                 acc[1] = fmaf(k.y, v, acc[1]);
@@ -253,34 +308,45 @@ __global__ void __launch_bounds__(256) retention_chunked_kernel(
                 acc[3] = fmaf(k.w, v, acc[3]);
             }
 #pragma unroll
-            for (int e = 0; e < 4; ++e) Ss[(r0 + e) * RC_COLS + lane] = fmaf(pw[n], Ss[(r0 + e) * RC_COLS + lane], acc[e]);
+            for (int e = 0; e < 4; ++e) Ss[(r0 + e) * cols + c] = fmaf(pw[n], Ss[(r0 + e) * cols + c], acc[e]);
         }
     }
     __syncthreads();
-    for (int i = tid; i < d * RC_COLS; i += 256) {
-        const int r = i / RC_COLS, c = i % RC_COLS;
-        if (c0 + c < dv) S[static_cast<size_t>(r) * dv + c0 + c] = Ss[i];
+    for (int i = tid; i < d4 * cols; i += 256) {
+        const int r = i / cols, cc = i % cols;
+        if (r < d && c0 + cc < dv) S[static_cast<size_t>(r) * dv + c0 + cc] = Ss[i];
     }
 }
 
-// The segments with at least qn_from new tokens (arguments as locus_retention_scan).
+// The segments with at least qn_from new tokens (arguments as locus_retention_scan); longest_new: the most new tokens
+// of a segment of the step (an upper bound will do: it sizes the first kernel's grid).
 extern "C" int locus_retention_chunked(const float* qkvg, int ld, float* state, const int* state_slots,
                                        const int* seg_q0, const int* seg_qn, int n_seg, const float* decay,
-                                       float k_scale, float* o_raw, int H, int d, int dv, int qn_from,
+                                       float k_scale, float* o_raw, int H, int d, int dv, int qn_from, int longest_new,
                                        cudaStream_t stream) {
-    if (n_seg <= 0) return 0;
-    if (H <= 0 || d <= 0 || d > 256 || dv <= 0 || n_seg > 65535 || ld < 2 * H * d + 2 * H * dv || qn_from < 1)
+    if (n_seg <= 0 || longest_new <= 0) return 0;
+    if (H <= 0 || d <= 0 || d > 256 || dv <= 0 || n_seg > 65535 || H > 65535 || ld < 2 * H * d + 2 * H * dv || qn_from < 1)
         return LOCUS_ERR_UNSUPPORTED;
-    const int col_groups = (dv + RC_COLS - 1) / RC_COLS;
-    const int d4 = (d + 3) & ~3;
-    const size_t smem = sizeof(float) * (2 * RC_CHUNK * (d4 + 4) + RC_CHUNK * RC_COLS + RC_CHUNK * (RC_CHUNK + 4) +
-                                         static_cast<size_t>(d4) * RC_COLS + RC_CHUNK + 4);
-    if (smem > 48 * 1024 &&
-        cudaFuncSetAttribute(retention_chunked_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize,
-                             static_cast<int>(smem)) != cudaSuccess)
+    const int d4 = (d + 3) & ~3, dvp = (dv + 31) & ~31;
+    const size_t smem1 = sizeof(float) * (2 * RC_CHUNK * (d4 + 4) + RC_CHUNK * (RC_CHUNK + 4) + static_cast<size_t>(RC_CHUNK) * dvp);
+    if (smem1 > 200 * 1024) return LOCUS_ERR_UNSUPPORTED;
+    if (smem1 > 48 * 1024 &&
+        cudaFuncSetAttribute(retention_intra_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                             static_cast<int>(smem1)) != cudaSuccess)
         return LOCUS_ERR_UNSUPPORTED;
-    locus_launch(retention_chunked_kernel, dim3(H * col_groups, n_seg), dim3(256), smem, stream, qkvg, ld, state,
-                 state_slots, seg_q0, seg_qn, decay, k_scale, o_raw, H, d, dv, col_groups, qn_from);
+    locus_launch(retention_intra_kernel, dim3((longest_new + RC_CHUNK - 1) / RC_CHUNK, H, n_seg), dim3(256), smem1, stream,
+                 qkvg, ld, seg_q0, seg_qn, decay, k_scale, o_raw, H, d, dv, qn_from);
+    // as few columns per block as it takes to give every SM a block
+    int cols = 32;
+    while (cols > 8 && static_cast<long long>(H) * ((dv + cols - 1) / cols) * n_seg < 148) cols >>= 1;
+    const int col_groups = (dv + cols - 1) / cols;
+    const size_t smem2 = sizeof(float) * (2 * RC_CHUNK * (d4 + 4) + RC_CHUNK * cols + static_cast<size_t>(d4) * cols + RC_CHUNK + 4);
+    if (smem2 > 48 * 1024 &&
+        cudaFuncSetAttribute(retention_inter_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                             static_cast<int>(smem2)) != cudaSuccess)
+        return LOCUS_ERR_UNSUPPORTED;
+    locus_launch(retention_inter_kernel, dim3(H * col_groups, n_seg), dim3(256), smem2, stream, qkvg, ld, state,
+                 state_slots, seg_q0, seg_qn, decay, k_scale, o_raw, H, d, dv, col_groups, cols, qn_from);
     return locus_launch_status();
 }
 

@@ -1378,14 +1378,16 @@ RETENTION_CHUNK_FROM = 16   # segments with at least this many new tokens go to 
 
 def retention_scan(qkvg: torch.Tensor, state: torch.Tensor, state_slots: torch.Tensor, seg_q0: torch.Tensor,
                    seg_qn: torch.Tensor, n_seg: int, decay: torch.Tensor, k_scale: float, o_raw: torch.Tensor, *,
-                   n_heads: int, dim: int, v_dim: int, short: bool = True, long: bool = True) -> None:
+                   n_heads: int, dim: int, v_dim: int, short: bool = True, long: bool = True,
+                   longest_new: int = 0) -> None:
     """The recurrence S = decay[h] * S + (k * k_scale) v^T, o = S^T q over every segment's new tokens in order,
     from and into ``state`` [n_slots, H, dim, v_dim] (float32) of the segment's slot.  ``qkvg`` [T, >= 2 H dim +
     2 H v_dim] float32 with the columns [q | k | v | gate]; ``o_raw`` [T, H * v_dim] float32.
 
     Two kernels share the segments: those with fewer than ``RETENTION_CHUNK_FROM`` new tokens are walked token by
     token (a warp per few columns of the state), the longer ones chunk by chunk as small matrix products; ``short``
-    / ``long`` say whether the step has segments of either kind at all (both True when the host cannot know)."""
+    / ``long`` say whether the step has segments of either kind at all (both True when the host cannot know);
+    ``longest_new``: the most new tokens of a segment (0: the rows of ``qkvg``)."""
     _cuda_c(qkvg, "qkvg")
     _cuda_c(state, "state")
     _cuda_c(o_raw, "o_raw")
@@ -1402,7 +1404,10 @@ def retention_scan(qkvg: torch.Tensor, state: torch.Tensor, state_slots: torch.T
     if long:
         code = _lib("retention").locus_retention_chunked(
             _p(qkvg), I(qkvg.stride(0)), _p(state), _p(state_slots), _p(seg_q0), _p(seg_qn), I(n_seg), _p(decay),
-            F(k_scale), _p(o_raw), I(n_heads), I(dim), I(v_dim), I(RETENTION_CHUNK_FROM if short else 1), _stream())
+            F(k_scale), _p(o_raw), I(n_heads), I(dim), I(v_dim), I(RETENTION_CHUNK_FROM if short else 1),
+            I(longest_new or qkvg.shape[0]), _stream())
+        if code == 0:
+            _count_launches(1)   # two kernels: the chunks' own terms, then the walk over the chunks
         _check(code, "retention_chunked", f"(heads {n_heads}, dim {dim}, v_dim {v_dim})")
 
 

@@ -71,7 +71,8 @@ class Retention(Mixer):
         short = not qn or min(qn) < K.RETENTION_CHUNK_FROM
         long = not qn or max(qn) >= K.RETENTION_CHUNK_FROM
         K.retention_scan(qkvg, state, batch.state_slots, batch.seg_q0, batch.seg_qn, batch.n_seg, self._decay,
-                         self.d ** -0.5, o_raw, n_heads=self.H, dim=self.d, v_dim=self.dv, short=short, long=long)
+                         self.d ** -0.5, o_raw, n_heads=self.H, dim=self.d, v_dim=self.dv, short=short, long=long,
+                         longest_new=max(qn) if qn else 0)
         o = rt.rows("retention.o", self.H * self.dv, rt.dtype, T)
         K.retention_gate_norm(o_raw, qkvg, 2 * self.H * self.d + self.H * self.dv, self.eps, o, n_heads=self.H,
                               v_dim=self.dv)

@@ -431,7 +431,7 @@ def heads_to_rows(src_hm, out, *, n_tokens, n_heads):
 
 
 def retention_scan(qkvg, state, state_slots, seg_q0, seg_qn, n_seg, decay, k_scale, o_raw, *, n_heads, dim, v_dim,
-                   short=True, long=True):
+                   short=True, long=True, longest_new=0):
     H, d, dv = n_heads, dim, v_dim
     for seg in range(n_seg):
         q0, qn, slot = int(seg_q0[seg]), int(seg_qn[seg]), int(state_slots[seg])
