@@ -33,7 +33,7 @@ def lalepel_config(z, n_layers):
     lat = {"type": "latent_attention", "mlp": moe, "mixer": {
         "heads": z["heads"], "dim": z["dim"], "rot_dim": z["rot"], "vdim": z["vdim"], "q_rank": z["q_rank"],
         "kv_rank": z["kv_rank"], "scale": (z["dim"] + z["rot"]) ** -0.5, "mask": {"size": z["window"]},
-        "rot": {"base": 10000.0, "dims": z["rot"], "scaling": {"factor": 8.0, "original": 4096, "fast": 32.0, "slow": 1.0}}}}
+        "rot": {"base": 10000.0, "dims": z["rot"], "scaling": {"factor": 4.0, "original": 8192, "fast": 32.0, "slow": 1.0}}}}
     ret = {"type": "retention", "mlp": moe, "mixer": {
         "heads": z["heads"], "dim": z["ret_dim"], "vdim": z["vdim"],
         "decay": [1.0 - 2.0 ** (-5 - 0.5 * i) for i in range(z["heads"])]}}

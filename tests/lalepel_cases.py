@@ -82,7 +82,7 @@ CONFIGS = {
     ]),
     # larger heads: latent rows of 160 elements, state rows beyond one lane's first register
     "wide": model(128, 211, [
-        with_mlp(latent(4, 32, 32, 32, 64, 128, window=100, scaling={"factor": 8.0, "original": 256, "fast": 32.0, "slow": 1.0}), DENSE(256)),
+        with_mlp(latent(4, 32, 32, 32, 64, 128, window=100, scaling={"factor": 6.0, "original": 256, "fast": 24.0, "slow": 1.5}), DENSE(256)),
         with_mlp(retention(2, 72, 40, [0.98, 0.9995]), MOE(8, 2, 64, shared=64)),
     ]),
 }

@@ -127,7 +127,7 @@ def _rand(shape, seed, scale=1.0, dtype=torch.float32):
 
 @pytest.mark.parametrize("dtype", DTYPES, ids=["f32", "bf16"])
 @pytest.mark.parametrize("kv_rank,rot_dim,heads,window", [(32, 8, 3, 12), (28, 6, 1, 0), (128, 32, 4, 100), (512, 64, 2, 0),
-                                                          (64, 16, 6, 40), (32, 0, 1, 7), (256, 48, 20, 33)])
+                                                          (64, 16, 5, 37), (32, 0, 1, 7), (256, 48, 20, 33)])
 def test_latent_attention_kernel_against_its_twin(kv_rank, rot_dim, heads, window, dtype):
     """latent_attn alone at several sizes, segments of one token and of many behind contexts that straddle pages,
     against the plain twin in float64."""

@@ -49,7 +49,7 @@ def test_frequencies_of_the_ramp_against_the_plain_formula():
     from locus_b200.parts.position import Rotary
 
     for dims, base, sc in ((8, 10000.0, {"factor": 4.0, "original": 64, "fast": 16.0, "slow": 2.0}),
-                           (32, 250000.0, {"factor": 8.0, "original": 2048, "fast": 32.0, "slow": 1.0}),
+                           (32, 50000.0, {"factor": 16.0, "original": 1024, "fast": 24.0, "slow": 2.0}),
                            (6, 77.0, None)):
         r = Rotary("p", head_dim=dims, theta=base, rot_dim=dims, interleaved=True, scaling=sc)
         f, mag = plain.rotary_frequencies(dims, base, sc)
