@@ -2,3 +2,4 @@ from .base import (ArchEntry, ConfigError, arch_name_of, archs, find_arch, load_
                    read_config_json, register_arch)
 from .qwen2_moe import Qwen2MoeConfig  # noqa: F401
 from .lalepel import LalepelConfig  # noqa: F401
+from .pozozen import PozozenConfig  # noqa: F401

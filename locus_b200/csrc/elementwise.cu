@@ -6,19 +6,25 @@
 // ---------------------------------------------------------------------------
 // Embedding: out[t, :] = table[tokens[t], :] as float32 (the residual stream is float32).
 __global__ void embed_rows_kernel(const int* __restrict__ tokens, const void* __restrict__ table,
-                                  int table_dt, float* __restrict__ out, int H) {
+                                  int table_dt, float* __restrict__ out, int H, int copies) {
     pdl_entry();
     pdl_trigger();
     const int t = blockIdx.x;
     const size_t row = static_cast<size_t>(tokens[t]) * H;
-    float* o = out + static_cast<size_t>(t) * H;
-    for (int i = threadIdx.x; i < H; i += blockDim.x) o[i] = ld_dyn(table, table_dt, row + i);
+    float* o = out + static_cast<size_t>(t) * H * copies;
+    for (int i = threadIdx.x; i < H; i += blockDim.x) {
+        const float v = ld_dyn(table, table_dt, row + i);
+        for (int c = 0; c < copies; ++c) o[c * H + i] = v;
+    }
 }
 
+// copies > 1: a row of out holds the table's row that many times, one behind the other (a model that keeps
+// several copies of the residual stream starts them all from the embedding).
 extern "C" int locus_embed_rows(const int* tokens, const void* table, int table_dt, float* out,
-                                int T, int H, cudaStream_t stream) {
+                                int T, int H, int copies, cudaStream_t stream) {
     if (T <= 0) return 0;
-    locus_launch(embed_rows_kernel, T, 256, 0, stream, tokens, table, table_dt, out, H);
+    if (copies < 1) return LOCUS_ERR_UNSUPPORTED;
+    locus_launch(embed_rows_kernel, T, 256, 0, stream, tokens, table, table_dt, out, H, copies);
     return locus_launch_status();
 }
 
@@ -535,5 +541,114 @@ extern "C" int locus_rmsnorm_add(const float* y, const void* w, int w_dt, float 
         locus_launch(rmsnorm_add_kernel<float>, n_rows, 256, 0, stream, y, static_cast<const float*>(w), eps, x, H);
     else
         return LOCUS_ERR_UNSUPPORTED;
+    return locus_launch_status();
+}
+
+// ---------------------------------------------------------------------------
+// Layer norm with weight and bias over a weighted sum of S copies of the residual stream:
+//     u = sum_s coef[s] x[r, s, :]   (coef null: the plain sum; S = 1 and coef null: the row itself)
+//     out[i, :] = (u - mean(u)) / sqrt(mean((u - mean)^2) + eps) * w + b,      r = rows ? rows[i] : i.
+// x [n, S, H] float32.  One block per row; the mean first, then the squared deviations from it; every sum in an order
+// that depends on H alone.
+#define LN_MAX_STREAMS 8
+
+__device__ __forceinline__ float block_sum_256(float v, float* part) {
+    v = warp_sum(v);
+    const int lane = threadIdx.x & 31, wid = threadIdx.x >> 5;
+    __syncthreads();  // part may still be read from the call before
+    if (lane == 0) part[wid] = v;
+    __syncthreads();
+    float tot = 0.f;
+    for (int k = 0; k < 8; ++k) tot += part[k];
+    return tot;
+}
+
+template <typename TO>
+__global__ void __launch_bounds__(256) layernorm_kernel(const float* __restrict__ x, int S,
+                                                        const float* __restrict__ coef, const void* __restrict__ w,
+                                                        const void* __restrict__ b, int w_dt, float eps,
+                                                        TO* __restrict__ out, const int* __restrict__ rows, int H) {
+    __shared__ float part[8];
+    pdl_entry();
+    pdl_trigger();
+    const int i = blockIdx.x;
+    const float* src = x + static_cast<size_t>(rows ? rows[i] : i) * S * H;
+    float cf[LN_MAX_STREAMS];
+#pragma unroll
+    for (int s = 0; s < LN_MAX_STREAMS; ++s) cf[s] = s < S ? (coef ? coef[s] : 1.0f) : 0.f;
+    auto u_at = [&](int j) {
+        float u = cf[0] * src[j];
+#pragma unroll
+        for (int s = 1; s < LN_MAX_STREAMS; ++s)
+            if (s < S) u = fmaf(cf[s], src[static_cast<size_t>(s) * H + j], u);
+        return u;
+    };
+    float sum = 0.f;
+    for (int j = threadIdx.x; j < H; j += 256) sum += u_at(j);
+    const float mean = block_sum_256(sum, part) / static_cast<float>(H);
+    float ss = 0.f;
+    for (int j = threadIdx.x; j < H; j += 256) {
+        const float dlt = u_at(j) - mean;
+        ss = fmaf(dlt, dlt, ss);
+    }
+    const float scale = 1.0f / sqrtf(block_sum_256(ss, part) / static_cast<float>(H) + eps);
+    TO* dst = out + static_cast<size_t>(i) * H;
+    for (int j = threadIdx.x; j < H; j += 256)
+        dst[j] = from_f<TO>(fmaf((u_at(j) - mean) * scale, ld_dyn(w, w_dt, j), ld_dyn(b, w_dt, j)));
+}
+
+extern "C" int locus_layernorm(const float* x, int n_streams, const float* coef, const void* w, const void* b, int w_dt,
+                               float eps, void* out, int out_dt, const int* rows, int n, int H, cudaStream_t stream) {
+    if (n <= 0) return 0;
+    if (n_streams < 1 || n_streams > LN_MAX_STREAMS || H <= 0) return LOCUS_ERR_UNSUPPORTED;
+    if (out_dt == LOCUS_DT_BF16)
+        locus_launch(layernorm_kernel<bf16>, n, 256, 0, stream, x, n_streams, coef, w, b, w_dt, eps,
+                     static_cast<bf16*>(out), rows, H);
+    else if (out_dt == LOCUS_DT_F32)
+        locus_launch(layernorm_kernel<float>, n, 256, 0, stream, x, n_streams, coef, w, b, w_dt, eps,
+                     static_cast<float*>(out), rows, H);
+    else
+        return LOCUS_ERR_UNSUPPORTED;
+    return locus_launch_status();
+}
+
+// ---------------------------------------------------------------------------
+// The write-back of a sublayer's output y into S copies of the residual stream, which are mixed among themselves
+// in the same pass:  x[r, t, :] <- sum_s mix[s, t] x[r, s, :] + out_coef[t] * y[r, :]   (all t at once from the old
+// copies; mix is indexed [from, to]).  S = 1, mix = [1]: x += out_coef[0] * y.
+__global__ void __launch_bounds__(256) stream_update_kernel(float* __restrict__ x, const float* __restrict__ y,
+                                                            const float* __restrict__ mix,
+                                                            const float* __restrict__ out_coef, int S, int H) {
+    __shared__ float m_s[LN_MAX_STREAMS * LN_MAX_STREAMS], c_s[LN_MAX_STREAMS];
+    pdl_entry();
+    pdl_trigger();
+    if (threadIdx.x < S * S) m_s[threadIdx.x] = mix[threadIdx.x];
+    if (threadIdx.x < S) c_s[threadIdx.x] = out_coef[threadIdx.x];
+    __syncthreads();
+    float* xr = x + static_cast<size_t>(blockIdx.x) * S * H;
+    const float* yr = y + static_cast<size_t>(blockIdx.x) * H;
+    for (int j = threadIdx.x; j < H; j += 256) {
+        float old[LN_MAX_STREAMS];
+#pragma unroll
+        for (int s = 0; s < LN_MAX_STREAMS; ++s) old[s] = s < S ? xr[static_cast<size_t>(s) * H + j] : 0.f;
+        const float yv = yr[j];
+#pragma unroll
+        for (int t = 0; t < LN_MAX_STREAMS; ++t) {
+            if (t < S) {
+                float v = c_s[t] * yv;
+#pragma unroll
+                for (int s = 0; s < LN_MAX_STREAMS; ++s)
+                    if (s < S) v = fmaf(m_s[s * S + t], old[s], v);
+                xr[static_cast<size_t>(t) * H + j] = v;
+            }
+        }
+    }
+}
+
+extern "C" int locus_stream_update(float* x, const float* y, const float* mix, const float* out_coef, int n_streams,
+                                   int n, int H, cudaStream_t stream) {
+    if (n <= 0) return 0;
+    if (n_streams < 1 || n_streams > LN_MAX_STREAMS || H <= 0) return LOCUS_ERR_UNSUPPORTED;
+    locus_launch(stream_update_kernel, n, 256, 0, stream, x, y, mix, out_coef, n_streams, H);
     return locus_launch_status();
 }

@@ -367,3 +367,61 @@ extern "C" int locus_route_small(const float* logits, int ld, int* ids, float* w
     locus_launch(route_small_kernel, 1, 32 * RS_WARPS, smem, stream, logits, ld, ids, wts, gamma, T, E, has_gate, o, lo);
     return locus_launch_status();
 }
+
+// ---------------------------------------------------------------------------
+// Experts without weights ("identity experts": the router's outputs from n_real on), whose output is their input.
+// After the layout is made: their tiles, which stand last in the tile lists (the lists are in expert order), are
+// taken off the lists, so that the grouped products never see them, and their rows of pair_out are written here:
+// pair_out[r, :] = wts[pair] * h[pair / k, :] for the rows r from offsets[n_real] on.
+template <typename TH, typename TP>
+__global__ void __launch_bounds__(256) moe_identity_kernel(const TH* __restrict__ h, const float* __restrict__ wts,
+                                                           const int* __restrict__ offsets,
+                                                           const int* __restrict__ sorted_pair, TP* __restrict__ pair_out,
+                                                           int n_pairs, int k, int H, int n_real,
+                                                           const int* __restrict__ tile_expert, int* __restrict__ n_tiles,
+                                                           const int* __restrict__ tile2_expert,
+                                                           int* __restrict__ n_tiles2, int max_tiles) {
+    pdl_entry();
+    pdl_trigger();
+    if (blockIdx.x == 0) {
+        // the first tile of an expert without weights is where a list ends
+        __shared__ int cut[2];
+        if (threadIdx.x < 2) cut[threadIdx.x] = 0x7fffffff;
+        __syncthreads();
+        const int n1 = min(*n_tiles, max_tiles), n2 = n_tiles2 ? min(*n_tiles2, max_tiles) : 0;
+        for (int i = threadIdx.x; i < n1; i += 256)
+            if (tile_expert[i] >= n_real) atomicMin(&cut[0], i);
+        for (int i = threadIdx.x; i < n2; i += 256)
+            if (tile2_expert[i] >= n_real) atomicMin(&cut[1], i);
+        __syncthreads();
+        if (threadIdx.x == 0 && cut[0] < n1) *n_tiles = cut[0];
+        if (threadIdx.x == 1 && cut[1] < n2) *n_tiles2 = cut[1];
+    }
+    const int first = offsets[n_real];
+    for (int r = first + blockIdx.x; r < n_pairs; r += gridDim.x) {
+        const int pair = sorted_pair[r];
+        const float w = wts[pair];
+        const TH* src = h + static_cast<size_t>(pair / k) * H;
+        TP* dst = pair_out + static_cast<size_t>(r) * H;
+        for (int j = threadIdx.x; j < H; j += 256) dst[j] = from_f<TP>(w * to_f(src[j]));
+    }
+}
+
+extern "C" int locus_moe_identity(const void* h, int h_dt, const float* wts, const int* offsets, const int* sorted_pair,
+                                  void* pair_out, int pair_dt, int n_pairs, int k, int H, int n_real,
+                                  const int* tile_expert, int* n_tiles, const int* tile2_expert, int* n_tiles2,
+                                  int max_tiles, cudaStream_t stream) {
+    if (n_pairs <= 0) return 0;
+    if (k <= 0 || H <= 0 || n_real < 0) return LOCUS_ERR_UNSUPPORTED;
+    const int blocks = n_pairs < 592 ? n_pairs : 592;
+#define IDENT(TH, TP)                                                                                                  \
+    locus_launch(moe_identity_kernel<TH, TP>, blocks, 256, 0, stream, static_cast<const TH*>(h), wts, offsets,         \
+                 sorted_pair, static_cast<TP*>(pair_out), n_pairs, k, H, n_real, tile_expert, n_tiles, tile2_expert,   \
+                 n_tiles2, max_tiles)
+    if (h_dt == LOCUS_DT_BF16 && pair_dt == LOCUS_DT_BF16) IDENT(bf16, bf16);
+    else if (h_dt == LOCUS_DT_F32 && pair_dt == LOCUS_DT_F32) IDENT(float, float);
+    else if (h_dt == LOCUS_DT_BF16 && pair_dt == LOCUS_DT_F32) IDENT(bf16, float);
+    else return LOCUS_ERR_UNSUPPORTED;
+#undef IDENT
+    return locus_launch_status();
+}

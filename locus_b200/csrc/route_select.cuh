@@ -6,11 +6,13 @@
 // How a token's experts are chosen from its router logits, as the reference's moe_select does it
 // (src/locus/model/llama.cpp:900-980): scores = softmax over all experts, or a sigmoid of each logit;
 // selection scores = scores (+ sel_bias, which never enters the weights); with n_group > 1 only the
-// n_group_used groups with the largest sum of their two best selection scores stay eligible (the others are
-// masked to -1e30); k rounds of arg-max with strict '>' (ties to the lowest index); weight = score / wsum *
+// n_group_used groups with the largest group score stay eligible (the others are masked to -1e30); a group's score
+// is the sum of its two best selection scores or, with GROUP_SCORE_BEST among the flags of score_fn, its best one; k rounds of arg-max with strict '>' (ties to the lowest index); weight = score / wsum *
 // scale, wsum = sum of the picked scores when renorm, else 1.
 #define SCORE_SOFTMAX 0
 #define SCORE_SIGMOID 1
+#define SCORE_FN_MASK 15      // score_fn: the score function in the low bits, flags above them
+#define GROUP_SCORE_BEST 16   // a group's score is its best selection score (else the sum of its two best)
 struct RouteOpts {
     int k, renorm, score_fn, n_group, n_group_used;
     float scale;
@@ -19,7 +21,7 @@ struct RouteOpts {
 
 __host__ inline bool route_opts_ok(const RouteOpts& o, int E) {
     if (E <= 0 || o.k <= 0 || o.k > E) return false;
-    if (o.score_fn != SCORE_SOFTMAX && o.score_fn != SCORE_SIGMOID) return false;
+    if ((o.score_fn & SCORE_FN_MASK) != SCORE_SOFTMAX && (o.score_fn & SCORE_FN_MASK) != SCORE_SIGMOID) return false;
     if (o.n_group < 1 || o.n_group > 32 || E % o.n_group != 0) return false;
     if (o.n_group > 1 && (o.n_group_used < 1 || o.n_group_used > o.n_group)) return false;
     return true;
@@ -35,7 +37,7 @@ __device__ __forceinline__ void select_token(const float* __restrict__ lg, float
                                              const RouteOpts o) {
     float* sel = p + E;
     const int k = o.k;
-    if (o.score_fn == SCORE_SOFTMAX) {
+    if ((o.score_fn & SCORE_FN_MASK) == SCORE_SOFTMAX) {
         float mx = -INFINITY;
         for (int x = lane; x < E; x += 32) {
             const float v = __ldcg(lg + x);
@@ -75,7 +77,7 @@ __device__ __forceinline__ void select_token(const float* __restrict__ lg, float
                     top2 = v;
                 }
             }
-            gs = top1 + (per > 1 ? top2 : 0.0f);
+            gs = top1 + ((per > 1 && !(o.score_fn & GROUP_SCORE_BEST)) ? top2 : 0.0f);
         }
         unsigned keep = 0;
         for (int r = 0; r < o.n_group_used; ++r) {

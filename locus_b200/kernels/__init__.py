@@ -199,16 +199,17 @@ F = ctypes.c_float
 
 
 # ---------------------------------------------------------------------------
-def embed_rows(tokens: torch.Tensor, table: torch.Tensor, out: torch.Tensor) -> None:
-    """out[t, :] = table[tokens[t], :] as float32."""
+def embed_rows(tokens: torch.Tensor, table: torch.Tensor, out: torch.Tensor, copies: int = 1) -> None:
+    """out[t, :] = table[tokens[t], :] as float32; ``copies`` > 1: the row that many times, one behind the other
+    (``out`` [T, copies * H])."""
     _i32(tokens, "tokens")
     _cuda_c(table, "table")
     _cuda_c(out, "out")
-    T, H = out.shape
+    T, H = out.shape[0], table.shape[1]
     _need(out.dtype == torch.float32, "embed_rows: out must be float32")
-    _need(tokens.numel() == T and table.shape[1] == H, "embed_rows: shape mismatch")
+    _need(tokens.numel() == T and copies >= 1 and out.shape[1] == H * copies, "embed_rows: shape mismatch")
     code = _lib("elementwise").locus_embed_rows(
-        _p(tokens), _p(table), I(dtype_code(table.dtype)), _p(out), I(T), I(H), _stream()
+        _p(tokens), _p(table), I(dtype_code(table.dtype)), _p(out), I(T), I(H), I(copies), _stream()
     )
     _check(code, "embed_rows")
 
@@ -486,7 +487,9 @@ def linear(x: torch.Tensor, w: torch.Tensor, out: torch.Tensor, *, w2: Optional[
     if x_rows is not None:
         _i32(x_rows, "x_rows")
     if layout is not None:
-        _need(w.dim() == 3 and w.shape[0] == layout.n_experts, "linear: grouped product needs w [E, N, K]")
+        # a layout may count experts without weights behind the ones with (their tiles are taken off its lists:
+        # moe_identity)
+        _need(w.dim() == 3 and w.shape[0] <= layout.n_experts, "linear: grouped product needs w [E, N, K]")
     if skinny_takes(x, w, M, layout):
         # bfloat16, up to 32 rows per tile: weight-streaming tensor-core kernel (csrc/gemm_skinny.cu)
         if layout is not None:
@@ -894,19 +897,23 @@ def attn_decode(q: torch.Tensor, pool: torch.Tensor, out: torch.Tensor, *, seg_q
 
 
 SCORE_FUNCTIONS = {"softmax": 0, "sigmoid": 1}
+# what a group of experts is judged by when only some groups stay eligible: the sum of its two best selection scores,
+# or its best one (a flag beside the score function's code, see csrc/route_select.cuh)
+GROUP_SCORES = {"top2": 0, "best": 16}
 
 
 def _route_rule(score_fn: str, sel_bias: Optional[torch.Tensor], n_group: int, n_group_used: int, n_experts: int,
-                what: str):
+                what: str, group_score: str = "top2"):
     """The arguments that say how experts are chosen, checked: (score code, bias pointer, groups, groups used)."""
     _need(score_fn in SCORE_FUNCTIONS, f"{what}: score function {score_fn!r} (known: {', '.join(SCORE_FUNCTIONS)})")
+    _need(group_score in GROUP_SCORES, f"{what}: group score {group_score!r} (known: {', '.join(GROUP_SCORES)})")
     if sel_bias is not None:
         _need(sel_bias.is_cuda and sel_bias.dtype == torch.float32 and sel_bias.is_contiguous()
               and sel_bias.numel() == n_experts, f"{what}: the selection bias must be float32 [n_experts]")
     _need(1 <= n_group <= 32 and n_experts % n_group == 0,
           f"{what}: {n_group} groups must divide {n_experts} experts (at most 32 groups)")
     _need(n_group == 1 or 1 <= n_group_used <= n_group, f"{what}: groups used must be within 1..{n_group}")
-    return I(SCORE_FUNCTIONS[score_fn]), _p(sel_bias), I(n_group), I(n_group_used)
+    return I(SCORE_FUNCTIONS[score_fn] | GROUP_SCORES[group_score]), _p(sel_bias), I(n_group), I(n_group_used)
 
 
 class RouterScratch:
@@ -924,11 +931,12 @@ def router_topk(h: torch.Tensor, w_router: torch.Tensor, w_gate: Optional[torch.
                 ids: torch.Tensor, wts: torch.Tensor, gamma: Optional[torch.Tensor], *, top_k: int,
                 renorm: bool, scale: float = 1.0, scratch: Optional[RouterScratch] = None, score_fn: str = "softmax",
                 sel_bias: Optional[torch.Tensor] = None, n_group: int = 1, n_group_used: int = 1,
-                logit_bias: Optional[torch.Tensor] = None) -> None:
+                logit_bias: Optional[torch.Tensor] = None, group_score: str = "top2") -> None:
     """Router: scores of all experts (``score_fn``: softmax over them, or a sigmoid of each logit), top-k by
     repeated arg-max, weights; and gamma = sigmoid(w_gate . h) when the shared expert is gated.  All in float32.
     ``sel_bias`` [E] is added to the scores for the selection only; with ``n_group`` > 1 only the
-    ``n_group_used`` groups of experts with the best two-score sums are eligible.  ``logit_bias`` [E] float32 is
+    ``n_group_used`` groups of experts with the best two-score sums (``group_score`` "best": with the best single
+    score) are eligible.  ``logit_bias`` [E] float32 is
     part of the logits (a router with a bias of its own): it enters the scores, the selection and the weights.
     ``scratch`` must hold T tokens of E (+1 with a gate) logits (made on the fly when None)."""
     _cuda_c(h, "h")
@@ -950,7 +958,7 @@ def router_topk(h: torch.Tensor, w_router: torch.Tensor, w_gate: Optional[torch.
         _p(h), I(dtype_code(h.dtype)), _p(w_router), I(dtype_code(w_router.dtype)), _p(w_gate),
         I(dtype_code(w_gate.dtype) if w_gate is not None else 0), _p(scratch.logits), _p(scratch.counters),
         _p(ids), _p(wts), _p(gamma), I(T), I(H), I(E), I(top_k), I(1 if renorm else 0), F(scale),
-        *_route_rule(score_fn, sel_bias, n_group, n_group_used, E, "router_topk"), _p(_logit_bias(logit_bias, E)),
+        *_route_rule(score_fn, sel_bias, n_group, n_group_used, E, "router_topk", group_score), _p(_logit_bias(logit_bias, E)),
         _stream()
     )
     _check(code, "router_topk", f"(H={H}, E={E}, k={top_k})")
@@ -988,7 +996,7 @@ def router_logits(h: torch.Tensor, w_all: torch.Tensor, logits: torch.Tensor,
 def router_select(logits: torch.Tensor, n_experts: int, has_gate: bool, ids: torch.Tensor, wts: torch.Tensor,
                   gamma: Optional[torch.Tensor], *, n_tokens: int, top_k: int, renorm: bool, scale: float = 1.0,
                   score_fn: str = "softmax", sel_bias: Optional[torch.Tensor] = None, n_group: int = 1,
-                  n_group_used: int = 1) -> None:
+                  n_group_used: int = 1, group_score: str = "top2") -> None:
     """Scores from the first ``n_experts`` columns of ``logits``, top-k by repeated arg-max,
     weights (the rule of :func:`router_topk`); gamma = sigmoid(column n_experts) when ``has_gate``."""
     _need(logits.is_cuda and logits.dtype == torch.float32 and logits.stride(1) == 1, "router_select: float32 logits")
@@ -1000,7 +1008,7 @@ def router_select(logits: torch.Tensor, n_experts: int, has_gate: bool, ids: tor
     code = _lib("moe_route").locus_router_select(
         _p(logits), I(logits.stride(0)), _p(ids), _p(wts), _p(gamma), I(n_tokens), I(n_experts), I(top_k),
         I(1 if has_gate else 0), I(1 if renorm else 0), F(scale),
-        *_route_rule(score_fn, sel_bias, n_group, n_group_used, n_experts, "router_select"), _stream()
+        *_route_rule(score_fn, sel_bias, n_group, n_group_used, n_experts, "router_select", group_score), _stream()
     )
     _check(code, "router_select", f"(E={n_experts}, k={top_k})")
 
@@ -1041,7 +1049,8 @@ def route_small_takes(n_tokens: int, top_k: int, n_experts: int) -> bool:
 def route_small(logits: torch.Tensor, n_experts: int, has_gate: bool, ids: torch.Tensor, wts: torch.Tensor,
                 gamma: Optional[torch.Tensor], layout: ExpertLayout, *, n_tokens: int, top_k: int, renorm: bool,
                 scale: float = 1.0, tile_m: Optional[int] = None, score_fn: str = "softmax",
-                sel_bias: Optional[torch.Tensor] = None, n_group: int = 1, n_group_used: int = 1) -> None:
+                sel_bias: Optional[torch.Tensor] = None, n_group: int = 1, n_group_used: int = 1,
+                group_score: str = "top2") -> None:
     """``router_select`` followed by ``moe_sort`` in one launch, for batches that
     ``route_small_takes``: same picks, weights and layout."""
     _need(route_small_takes(n_tokens, top_k, n_experts), "route_small: batch too large")
@@ -1060,7 +1069,7 @@ def route_small(logits: torch.Tensor, n_experts: int, has_gate: bool, ids: torch
     code = _lib("moe_route").locus_route_small(
         _p(logits), I(logits.stride(0)), _p(ids), _p(wts), _p(gamma), I(n_tokens), I(n_experts), I(top_k),
         I(1 if has_gate else 0), I(1 if renorm else 0), F(scale),
-        *_route_rule(score_fn, sel_bias, n_group, n_group_used, n_experts, "route_small"), I(layout.tile_m), _p(layout.counts),
+        *_route_rule(score_fn, sel_bias, n_group, n_group_used, n_experts, "route_small", group_score), I(layout.tile_m), _p(layout.counts),
         _p(layout.offsets), _p(layout.sorted_pair), _p(layout.pair_pos), _p(layout.tile_expert),
         _p(layout.tile_row0), _p(layout.tile_rows), _p(layout.n_tiles), _stream()
     )
@@ -1071,7 +1080,8 @@ def route_fused_small(h: torch.Tensor, w_all: torch.Tensor, logits: torch.Tensor
                       ids: torch.Tensor, wts: torch.Tensor, gamma: Optional[torch.Tensor], layout: ExpertLayout,
                       counter: torch.Tensor, *, n_tokens: int, top_k: int, renorm: bool, scale: float = 1.0,
                       tile_m: Optional[int] = None, score_fn: str = "softmax", sel_bias: Optional[torch.Tensor] = None,
-                      n_group: int = 1, n_group_used: int = 1, logit_bias: Optional[torch.Tensor] = None) -> None:
+                      n_group: int = 1, n_group_used: int = 1, logit_bias: Optional[torch.Tensor] = None,
+                      group_score: str = "top2") -> None:
     """:func:`router_logits` (with ``logit_bias`` as its bias) followed by :func:`route_small` in ONE launch, for batches that ``route_small_takes``:
     the same logits (the same kernel computes them), picks, weights and layout.  ``counter``: one int32 that is
     zero before the call and zero after it."""
@@ -1098,7 +1108,7 @@ def route_fused_small(h: torch.Tensor, w_all: torch.Tensor, logits: torch.Tensor
     code = _lib("gemm_skinny").locus_router_fused_small(
         _p(h), _p(w_all), _p(logits), I(logits.stride(0)), _p(counter), _p(ids), _p(wts), _p(gamma), I(T), I(H),
         LL(h.stride(0)), I(n_experts), I(top_k), I(1 if has_gate else 0), I(1 if renorm else 0), F(scale),
-        *_route_rule(score_fn, sel_bias, n_group, n_group_used, n_experts, "route_fused_small"), I(layout.tile_m),
+        *_route_rule(score_fn, sel_bias, n_group, n_group_used, n_experts, "route_fused_small", group_score), I(layout.tile_m),
         _p(layout.counts), _p(layout.offsets), _p(layout.sorted_pair), _p(layout.pair_pos), _p(layout.tile_expert),
         _p(layout.tile_row0), _p(layout.tile_rows), _p(layout.n_tiles), _p(_logit_bias(logit_bias, n)), _stream()
     )
@@ -1426,6 +1436,206 @@ def retention_gate_norm(o_raw: torch.Tensor, qkvg: torch.Tensor, gate_offset: in
                                                        _p(out), I(dtype_code(out.dtype)), I(T), I(n_heads), I(v_dim),
                                                        _stream())
     _check(code, "retention_gate_norm")
+
+
+# ---------------------------------------------------------------------------
+# several copies of the residual stream, layer norm
+
+MAX_STREAMS = 8
+
+
+def layernorm(x: torch.Tensor, w: torch.Tensor, b: torch.Tensor, eps: float, out: torch.Tensor,
+              rows: Optional[torch.Tensor] = None, n_streams: int = 1, coef: Optional[torch.Tensor] = None) -> None:
+    """out[i] = layer norm (weight ``w``, bias ``b``; mean and variance in float32) of u = sum_s coef[s] * x[r, s, :],
+    r = rows[i] if ``rows`` else i.  ``x`` [n, n_streams * H] float32 holds ``n_streams`` copies of the residual stream
+    per row; ``coef`` [n_streams] float32, None: the plain sum (with one stream: the row itself)."""
+    _cuda_c(x, "x")
+    _cuda_c(out, "out")
+    n, H = out.shape
+    _need(x.dtype == torch.float32 and x.shape[1] == n_streams * H and 1 <= n_streams <= MAX_STREAMS,
+          "layernorm: x must be float32 [n, n_streams * H]")
+    _need(w.numel() == H and b.numel() == H and w.dtype == b.dtype and w.is_cuda and b.is_cuda, "layernorm: w, b [H]")
+    if coef is not None:
+        _need(coef.is_cuda and coef.dtype == torch.float32 and coef.numel() == n_streams, "layernorm: coef [n_streams] float32")
+    if rows is not None:
+        _i32(rows, "rows")
+        _need(rows.numel() == n, "layernorm: rows/out mismatch")
+    else:
+        _need(x.shape[0] >= n, "layernorm: x/out mismatch")
+    code = _lib("elementwise").locus_layernorm(_p(x), I(n_streams), _p(coef), _p(w), _p(b), I(dtype_code(w.dtype)), F(eps),
+                                               _p(out), I(dtype_code(out.dtype)), _p(rows), I(n), I(H), _stream())
+    _check(code, "layernorm")
+
+
+def stream_update(x: torch.Tensor, y: torch.Tensor, mix: torch.Tensor, out_coef: torch.Tensor, n_streams: int) -> None:
+    """x[r, t, :] <- sum_s mix[s, t] * x[r, s, :] + out_coef[t] * y[r, :] for the rows of ``y``, every copy t at once
+    from the old copies.  ``x`` [>= n, n_streams * H] and ``y`` [n, H] float32; ``mix`` [n_streams, n_streams] (indexed
+    [from, to]) and ``out_coef`` [n_streams] float32."""
+    _cuda_c(x, "x")
+    _cuda_c(y, "y")
+    n, H = y.shape
+    _need(x.dtype == y.dtype == torch.float32 and x.shape[0] >= n and x.shape[1] == n_streams * H
+          and 1 <= n_streams <= MAX_STREAMS, "stream_update: x [n, n_streams * H], y [n, H] float32")
+    _need(mix.is_cuda and out_coef.is_cuda and mix.dtype == out_coef.dtype == torch.float32
+          and mix.numel() == n_streams * n_streams and out_coef.numel() == n_streams and mix.is_contiguous(),
+          "stream_update: mix [S, S], out_coef [S] float32")
+    code = _lib("elementwise").locus_stream_update(_p(x), _p(y), _p(mix), _p(out_coef), I(n_streams), I(n), I(H), _stream())
+    _check(code, "stream_update")
+
+
+def moe_identity(h: torch.Tensor, wts: torch.Tensor, layout: ExpertLayout, pair_out: torch.Tensor, *, n_pairs: int,
+                 top_k: int, n_real: int) -> None:
+    """Experts from ``n_real`` on have no weights and pass their input through: their tiles are taken off the layout's
+    tile lists and their rows are written, pair_out[r] = wts[pair] * h[pair // top_k] for the layout's rows r of
+    those experts.  To be called behind the call that filled the layout and before the grouped products."""
+    _cuda_c(h, "h")
+    _cuda_c(pair_out, "pair_out")
+    H = h.shape[1]
+    _need(wts.dtype == torch.float32 and wts.numel() >= n_pairs and pair_out.shape[0] >= n_pairs
+          and pair_out.shape[1] == H and 0 <= n_real <= layout.n_experts, "moe_identity: shapes")
+    second = layout.tile2_m > 0
+    code = _lib("moe_route").locus_moe_identity(
+        _p(h), I(dtype_code(h.dtype)), _p(wts), _p(layout.offsets), _p(layout.sorted_pair), _p(pair_out),
+        I(dtype_code(pair_out.dtype)), I(n_pairs), I(top_k), I(H), I(n_real), _p(layout.tile_expert), _p(layout.n_tiles),
+        _p(layout.tile2_expert if second else None), _p(layout.n_tiles2 if second else None), I(layout.max_tiles),
+        _stream())
+    _check(code, "moe_identity")
+
+
+# ---------------------------------------------------------------------------
+# gated linear recurrence and the mixers around it
+
+RECURRENCE_MAX_DIM = 256
+RECURRENCE_CHUNK_FROM = 16   # segments with at least this many new tokens go to the chunked kernels
+
+
+def _f32c(t: torch.Tensor, name: str) -> None:
+    _need(t.is_cuda and t.dtype == torch.float32 and t.stride(-1) == 1, f"{name} must be a float32 CUDA tensor with unit stride")
+
+
+def gated_recurrence(q: torch.Tensor, off_q: int, k: torch.Tensor, off_k: int, v: torch.Tensor, off_v: int,
+                     keep: torch.Tensor, take: torch.Tensor, state: torch.Tensor, state_offset: int,
+                     state_slots: torch.Tensor, seg_q0: torch.Tensor, seg_qn: torch.Tensor, n_seg: int, out: torch.Tensor,
+                     *, n_heads: int, heads_per_group: int, dim: int, v_dim: int, ones: bool = False,
+                     q_scale: float = 1.0, short: bool = True, long: bool = True, longest_new: int = 0) -> None:
+    """S = keep[t, h] * S + take[t, h] * k v^T, o = S^T (q * q_scale) per request and head over every segment's new
+    tokens in order, from and into the request's state slot.  ``q``, ``k``, ``v``: float32 row matrices [T, .] in which
+    head h's q and k start at column ``off_q`` / ``off_k`` + (h // heads_per_group) * dim and its v at ``off_v`` + h *
+    v_dim.  ``keep``, ``take`` [T, n_heads] float32.  ``state`` [n_slots, floats per slot] float32: head h's matrix
+    [dim, v_dim (+1)] starts ``state_offset`` + h * dim * (v_dim (+1)) floats into a slot.  ``ones``: the state has one
+    column more, whose v is 1 (the recurrence of k alone); ``out`` [T, n_heads * (v_dim (+1))] float32.
+
+    Segments with fewer than ``RECURRENCE_CHUNK_FROM`` new tokens are walked token by token, longer ones chunk by chunk
+    as small matrix products; ``short`` / ``long`` say whether the step has segments of either kind (both True when the
+    host cannot know); ``longest_new``: the most new tokens of a segment (0: the rows of ``out``)."""
+    for t, name in ((q, "q"), (k, "k"), (v, "v"), (keep, "keep"), (take, "take"), (out, "out")):
+        _f32c(t, f"gated_recurrence: {name}")
+    _cuda_c(state, "state")
+    _i32(state_slots, "state_slots")
+    dvx = v_dim + (1 if ones else 0)
+    _need(state.dtype == torch.float32 and state.dim() == 2
+          and state_offset + n_heads * dim * dvx <= state.shape[1], "gated_recurrence: the state does not hold the heads")
+    _need(keep.shape[1] == n_heads and take.shape[1] == n_heads and keep.is_contiguous() and take.is_contiguous(),
+          "gated_recurrence: keep, take [T, n_heads]")
+    _need(out.shape[1] == n_heads * dvx and out.is_contiguous(), "gated_recurrence: out [T, n_heads * columns]")
+    _need(dim <= RECURRENCE_MAX_DIM, f"gated_recurrence: dim {dim} exceeds {RECURRENCE_MAX_DIM}")
+    args = (_p(q), I(q.stride(0)), I(off_q), _p(k), I(k.stride(0)), I(off_k), _p(v), I(v.stride(0)), I(off_v), _p(keep),
+            _p(take), ctypes.c_void_p(state.data_ptr() + 4 * state_offset), LL(state.stride(0)), _p(state_slots),
+            _p(seg_q0), _p(seg_qn), I(n_seg), F(q_scale), _p(out), I(out.stride(0)), I(n_heads), I(heads_per_group),
+            I(dim), I(v_dim), I(1 if ones else 0))
+    what = f"(heads {n_heads}, dim {dim}, v_dim {v_dim})"
+    if short:
+        code = _lib("recurrence").locus_gated_scan(*args, I(RECURRENCE_CHUNK_FROM if long else 0), _stream())
+        _check(code, "gated_scan", what)
+    if long:
+        code = _lib("recurrence").locus_gated_chunked(*args, I(RECURRENCE_CHUNK_FROM if short else 1),
+                                                      I(longest_new or out.shape[0]), _stream())
+        if code == 0:
+            _count_launches(1)   # two kernels: the chunks' own terms, then the walk over the chunks
+        _check(code, "gated_chunked", what)
+
+
+def mlstm_gates(proj: torch.Tensor, off_i: int, off_f: int, cap: float, state: torch.Tensor, m_offset: int,
+                state_slots: torch.Tensor, seg_q0: torch.Tensor, seg_qn: torch.Tensor, n_seg: int, keep: torch.Tensor,
+                take: torch.Tensor, m_out: torch.Tensor, *, n_heads: int) -> None:
+    """From the pre-activations in columns ``off_i`` + h and ``off_f`` + h of ``proj`` (float32 rows): i = cap *
+    tanh(z_i / cap), f = logsigmoid(cap * tanh(z_f / cap)), the running maximum m_t = max(f + m_(t-1), i) (carried in
+    the state slot at ``m_offset`` + h), keep = exp(f + m_(t-1) - m_t), take = exp(i - m_t); ``m_out`` gets m_t.  All
+    [T, n_heads] float32."""
+    _f32c(proj, "mlstm_gates: proj")
+    _cuda_c(state, "state")
+    for t in (keep, take, m_out):
+        _need(t.is_cuda and t.dtype == torch.float32 and t.is_contiguous() and t.shape[1] == n_heads, "mlstm_gates: [T, n_heads] float32")
+    _need(state.dtype == torch.float32 and state.dim() == 2 and m_offset + n_heads <= state.shape[1], "mlstm_gates: state")
+    code = _lib("mlstm").locus_mlstm_gates(_p(proj), I(proj.stride(0)), I(off_i), I(off_f), F(cap),
+                                           ctypes.c_void_p(state.data_ptr() + 4 * m_offset), LL(state.stride(0)),
+                                           _p(state_slots), _p(seg_q0), _p(seg_qn), I(n_seg), _p(keep), _p(take), _p(m_out),
+                                           I(n_heads), _stream())
+    _check(code, "mlstm_gates")
+
+
+def mlstm_out(o_raw: torch.Tensor, m_t: torch.Tensor, proj: torch.Tensor, off_g: int, w: torch.Tensor, eps: float,
+              out: torch.Tensor, *, n_heads: int, v_dim: int) -> None:
+    """o_raw [T, n_heads * (v_dim + 1)]: per head the numerator and, behind it, n . q.  out[t, h, :] = (numerator /
+    (max(|n . q|, exp(-m_t)) + 1e-6)) / its root mean square * w[h, :] * sigmoid(gate), the gate being the columns of
+    ``proj`` from ``off_g`` on."""
+    _f32c(o_raw, "mlstm_out: o_raw")
+    _f32c(proj, "mlstm_out: proj")
+    _cuda_c(out, "out")
+    T = out.shape[0]
+    _need(o_raw.is_contiguous() and o_raw.shape[1] == n_heads * (v_dim + 1) and out.shape[1] == n_heads * v_dim
+          and w.numel() == n_heads * v_dim and m_t.dtype == torch.float32 and m_t.is_contiguous(), "mlstm_out: shapes")
+    code = _lib("mlstm").locus_mlstm_out(_p(o_raw), _p(m_t), _p(proj), I(proj.stride(0)), I(off_g), _p(w),
+                                         I(dtype_code(w.dtype)), F(eps), _p(out), I(dtype_code(out.dtype)), I(T),
+                                         I(n_heads), I(v_dim), _stream())
+    _check(code, "mlstm_out")
+
+
+SSM_MAX_TAPS = 16
+
+
+def ssm_conv(proj: torch.Tensor, off_xbc: int, off_dt: int, conv_w: torch.Tensor, conv_b: torch.Tensor,
+             dt_bias: torch.Tensor, a_log: torch.Tensor, state: torch.Tensor, conv_offset: int,
+             state_slots: torch.Tensor, seg_q0: torch.Tensor, seg_qn: torch.Tensor, n_seg: int, act: torch.Tensor,
+             keep: torch.Tensor, take: torch.Tensor, *, n_heads: int, longest_new: int = 0) -> None:
+    """act[t, c] = silu(conv_b[c] + sum_j conv_w[c, j] * input(t - (taps - 1) + j, c)), the inputs being the columns of
+    ``proj`` from ``off_xbc`` on and, before a portion's first token, the ``taps`` - 1 inputs that the request's
+    state slot holds ([channels, taps - 1] floats from ``conv_offset`` on; they move on by the portion's tokens in the
+    same call).  Also dt = softplus(proj[t, off_dt + h] + dt_bias[h]), keep = exp(-exp(a_log[h]) * dt), take = dt."""
+    _f32c(proj, "ssm_conv: proj")
+    _cuda_c(state, "state")
+    channels, taps = conv_w.shape
+    _need(conv_w.is_contiguous() and conv_b.numel() == channels and conv_w.dtype == conv_b.dtype and 1 <= taps <= SSM_MAX_TAPS,
+          "ssm_conv: conv weights [channels, taps], bias [channels]")
+    _need(dt_bias.numel() == n_heads and a_log.numel() == n_heads and dt_bias.dtype == a_log.dtype, "ssm_conv: dt_bias, A_log [heads]")
+    _need(state.dtype == torch.float32 and state.dim() == 2 and conv_offset + channels * (taps - 1) <= state.shape[1], "ssm_conv: state")
+    for t, wdt in ((act, channels), (keep, n_heads), (take, n_heads)):
+        _need(t.is_cuda and t.dtype == torch.float32 and t.is_contiguous() and t.shape[1] == wdt, "ssm_conv: outputs")
+    code = _lib("state_space").locus_ssm_conv(
+        _p(proj), I(proj.stride(0)), I(off_xbc), I(off_dt), _p(conv_w), _p(conv_b), I(dtype_code(conv_w.dtype)),
+        _p(dt_bias), _p(a_log), I(dtype_code(a_log.dtype)), ctypes.c_void_p(state.data_ptr() + 4 * conv_offset),
+        LL(state.stride(0)), _p(state_slots), _p(seg_q0), _p(seg_qn), I(n_seg), I(longest_new or act.shape[0]), _p(act),
+        _p(keep), _p(take), I(channels), I(taps), I(n_heads), _stream())
+    if code == 0 and taps > 1:
+        _count_launches(1)
+    _check(code, "ssm_conv")
+
+
+def ssm_out(y: torch.Tensor, act: torch.Tensor, proj: torch.Tensor, off_z: int, d_skip: torch.Tensor, w: torch.Tensor,
+            eps: float, out: torch.Tensor, *, parts: int, v_dim: int) -> None:
+    """out[t] = ((y[t] + d_skip[head] * x[t]) * silu(z[t])), each of ``parts`` equal parts of the row divided by its
+    root mean square, times ``w``; x: the first columns of ``act``, z: the columns of ``proj`` from ``off_z`` on."""
+    _f32c(y, "ssm_out: y")
+    _f32c(act, "ssm_out: act")
+    _f32c(proj, "ssm_out: proj")
+    _cuda_c(out, "out")
+    T, inner = out.shape
+    _need(y.is_contiguous() and act.is_contiguous() and y.shape[1] == inner and act.shape[1] >= inner
+          and w.numel() == inner and d_skip.numel() * v_dim == inner and inner % parts == 0, "ssm_out: shapes")
+    code = _lib("state_space").locus_ssm_out(_p(y), _p(act), I(act.shape[1]), _p(proj), I(proj.stride(0)), I(off_z),
+                                             _p(d_skip), I(dtype_code(d_skip.dtype)), _p(w), I(dtype_code(w.dtype)), F(eps),
+                                             _p(out), I(dtype_code(out.dtype)), I(T), I(parts), I(inner), I(v_dim), _stream())
+    _check(code, "ssm_out")
 
 
 def apply_penalties(logits: torch.Tensor, history: torch.Tensor, repeat: torch.Tensor,

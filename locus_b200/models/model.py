@@ -107,7 +107,7 @@ class Model:
         """Run the step's tokens through every layer call; float32 logits [n_want, vocab]."""
         rt = self.rt
         T = batch.T
-        x = rt.rows("model.x", self.plan.hidden_size, torch.float32, T)
+        x = rt.rows("model.x", self.plan.hidden_size * self.plan.residual_streams, torch.float32, T)
         self.embedding.forward(batch.tokens, x)
         order = self.plan.order
         for i, (call, cache) in enumerate(zip(order, caches)):

@@ -11,6 +11,11 @@ the residual stream (src/locus/model/llama.cpp:487-490).
 
 The three projections are one product against the stacked weight [(heads + 2 kv_heads) *
 head_dim, hidden]; that is layout only.  Scores, softmax and the weighted sum are float32.
+
+Values may have another size than queries and keys (``v_dim``), and either size need not be one the attention
+kernels take: the heads are then laid out at the next multiple of 16 that holds both, with zero rows in the stacked
+weight and bias and zero columns in the output projection, so that the padding is exact zeros in q, k, v and the cache
+and contributes nothing to a score or an output.  The score's factor is then the caller's (``softmax_scale``).
 """
 from __future__ import annotations
 
@@ -21,6 +26,7 @@ import torch
 
 from .. import kernels as K
 from .base import Mixer, PagedKvSpec, PartSpec, StepPlan, TensorSource, make_part, register_mixer
+from .position import NoPosition as _NoRotation
 
 CHUNK_TILE = 16  # queries per work item of the CUDA-core chunk kernel
 
@@ -62,19 +68,39 @@ class AttentionTiles(StepPlan):
                 "decode_items": (o1, n1, None), "n_decode_items": n1}
 
 
+# tensor names below an attention's prefix, by role; an architecture with other names passes its own
+NAMES = {"q": "q_proj.weight", "k": "k_proj.weight", "v": "v_proj.weight", "o": "o_proj.weight",
+         "q_bias": "q_proj.bias", "k_bias": "k_proj.bias", "v_bias": "v_proj.bias", "o_bias": "o_proj.bias"}
+
+
 class Attention(Mixer):
+    can_overwrite = True
+
     def __init__(self, prefix: str, *, hidden: int, n_heads: int, n_kv_heads: int, head_dim: int,
                  qkv_bias: bool, o_bias: bool = False, window: int = 0,
-                 position: PartSpec = PartSpec("none"), softmax_scale: Optional[float] = None) -> None:
+                 position: PartSpec = PartSpec("none"), softmax_scale: Optional[float] = None,
+                 v_dim: Optional[int] = None, out_scale: float = 1.0, names: Optional[dict] = None) -> None:
+        """``v_dim``: the values' size per head where it is not ``head_dim``.  ``out_scale``: a factor on the mixer's
+        output (a mixer that runs beside another one).  ``names``: tensor names below the prefix where they differ
+        from ``NAMES``."""
         super().__init__(prefix)
         if n_heads % n_kv_heads:
             raise ValueError(f"attention: {n_heads} heads are not a multiple of {n_kv_heads} kv heads")
-        if head_dim % 16 or not (16 <= head_dim <= 256):
-            raise ValueError(f"attention: head_dim {head_dim} is not a multiple of 16 in 16..256 "
-                             "(the attention kernels take no other head size)")
+        self.qk_dim, self.v_dim = int(head_dim), int(v_dim if v_dim is not None else head_dim)
+        # the size the kernels see: a multiple of 16 that holds queries, keys and values
+        laid = -(-max(self.qk_dim, self.v_dim) // 16) * 16
+        self.padded = laid != self.qk_dim or laid != self.v_dim
+        if not (16 <= laid <= 256):
+            raise ValueError(f"attention: heads of {self.qk_dim} (values {self.v_dim}) exceed 256 "
+                             "(the attention kernels take no larger head)")
+        if self.padded and not isinstance(make_part("position", position, prefix + ".position"), _NoRotation):
+            raise ValueError("attention: heads that are padded to the kernels' sizes take no rotation")
+        head_dim = laid
         self.hidden, self.n_heads, self.n_kv_heads, self.head_dim = hidden, n_heads, n_kv_heads, head_dim
         self.qkv_bias, self.o_bias, self.window = bool(qkv_bias), bool(o_bias), int(window)
-        self.scale = float(softmax_scale) if softmax_scale is not None else 1.0 / math.sqrt(head_dim)
+        self.scale = float(softmax_scale) if softmax_scale is not None else 1.0 / math.sqrt(self.qk_dim)
+        self.out_scale = float(out_scale)
+        self.names = {**NAMES, **(names or {})}
         self.position = make_part("position", position, prefix + ".position")
         self.q_dim = n_heads * head_dim
         self.kv_dim = n_kv_heads * head_dim
@@ -83,25 +109,71 @@ class Attention(Mixer):
         return [self.position]
 
     # -- weights ------------------------------------------------------------
+    def _stored(self):
+        """(role, rows as stored) of the three projections."""
+        return [("q", self.n_heads * self.qk_dim), ("k", self.n_kv_heads * self.qk_dim), ("v", self.n_kv_heads * self.v_dim)]
+
     def param_shapes(self):
-        shapes = {"wqkv": (self.q_dim + 2 * self.kv_dim, self.hidden), "wo": (self.hidden, self.q_dim)}
-        if self.qkv_bias:
-            shapes["bqkv"] = (self.q_dim + 2 * self.kv_dim,)
+        if self.padded and "wqkv" not in self.params:
+            # loaded as stored, laid out for the kernels in bind
+            shapes = {f"w{r}_stored": (n, self.hidden) for r, n in self._stored()}
+            shapes["wo_stored"] = (self.hidden, self.n_heads * self.v_dim)
+            if self.qkv_bias:
+                shapes.update({f"b{r}_stored": (n,) for r, n in self._stored()})
+        elif self.padded:
+            return {n: tuple(t.shape) for n, t in self.params.items()}
+        else:
+            shapes = {"wqkv": (self.q_dim + 2 * self.kv_dim, self.hidden), "wo": (self.hidden, self.q_dim)}
+            if self.qkv_bias:
+                shapes["bqkv"] = (self.q_dim + 2 * self.kv_dim,)
         if self.o_bias:
             shapes["bo"] = (self.hidden,)
         return shapes
 
     def sources(self):
-        p = self.prefix
-        rows = [("q_proj", 0, self.q_dim), ("k_proj", self.q_dim, self.kv_dim),
-                ("v_proj", self.q_dim + self.kv_dim, self.kv_dim)]
-        out = [TensorSource(f"{p}.{n}.weight", (size, self.hidden), "wqkv", row0) for n, row0, size in rows]
-        if self.qkv_bias:
-            out += [TensorSource(f"{p}.{n}.bias", (size,), "bqkv", row0, "bias") for n, row0, size in rows]
-        out.append(TensorSource(f"{p}.o_proj.weight", (self.hidden, self.q_dim), "wo"))
+        p, nm = self.prefix, self.names
+        if self.padded:
+            out = [TensorSource(f"{p}.{nm[r]}", (n, self.hidden), f"w{r}_stored") for r, n in self._stored()]
+            if self.qkv_bias:
+                out += [TensorSource(f"{p}.{nm[r + '_bias']}", (n,), f"b{r}_stored", 0, "bias") for r, n in self._stored()]
+            out.append(TensorSource(f"{p}.{nm['o']}", (self.hidden, self.n_heads * self.v_dim), "wo_stored"))
+        else:
+            rows = [("q", 0, self.q_dim), ("k", self.q_dim, self.kv_dim), ("v", self.q_dim + self.kv_dim, self.kv_dim)]
+            out = [TensorSource(f"{p}.{nm[r]}", (size, self.hidden), "wqkv", row0) for r, row0, size in rows]
+            if self.qkv_bias:
+                out += [TensorSource(f"{p}.{nm[r + '_bias']}", (size,), "bqkv", row0, "bias") for r, row0, size in rows]
+            out.append(TensorSource(f"{p}.{nm['o']}", (self.hidden, self.q_dim), "wo"))
         if self.o_bias:
-            out.append(TensorSource(f"{p}.o_proj.bias", (self.hidden,), "bo", 0, "bias"))
+            out.append(TensorSource(f"{p}.{nm['o_bias']}", (self.hidden,), "bo", 0, "bias"))
         return out
+
+    def bind(self, rt) -> None:
+        self._scale = None
+        if self.out_scale != 1.0:
+            self._scale = rt.shared_object(("row_scale", self.out_scale), lambda: torch.full(
+                (rt.max_tokens,), self.out_scale, dtype=torch.float32, device=rt.device))
+        if not self.padded or "wqkv" in self.params:
+            return
+        # the stored heads at the kernels' head size: zero rows behind every head of q, k and v, zero columns behind
+        # every head of the output projection
+        D, P = self.head_dim, self.params
+        some = P["wq_stored"]
+        wqkv = torch.zeros((self.q_dim + 2 * self.kv_dim, self.hidden), dtype=some.dtype, device=some.device)
+        bqkv = torch.zeros((self.q_dim + 2 * self.kv_dim,), dtype=P["bq_stored"].dtype, device=some.device) if self.qkv_bias else None
+        row0 = 0
+        for r, heads, size in (("q", self.n_heads, self.qk_dim), ("k", self.n_kv_heads, self.qk_dim),
+                               ("v", self.n_kv_heads, self.v_dim)):
+            wqkv[row0:row0 + heads * D].view(heads, D, self.hidden)[:, :size] = P[f"w{r}_stored"].view(heads, size, self.hidden)
+            if bqkv is not None:
+                bqkv[row0:row0 + heads * D].view(heads, D)[:, :size] = P[f"b{r}_stored"].view(heads, size)
+            row0 += heads * D
+        wo = torch.zeros((self.hidden, self.q_dim), dtype=some.dtype, device=some.device)
+        wo.view(self.hidden, self.n_heads, D)[:, :, : self.v_dim] = P["wo_stored"].view(self.hidden, self.n_heads, self.v_dim)
+        for name in [n for n in P if n.endswith("_stored")]:
+            del P[name]
+        P["wqkv"], P["wo"] = wqkv, wo
+        if bqkv is not None:
+            P["bqkv"] = bqkv
 
     def kernel_modules(self, dtype):
         return ["elementwise", "gemm_simt", "gemv", "attention"] + (["gemm_skinny", "gemm_tc", "attention_mma", "attention_tc", "attention_gqa"] if dtype == torch.bfloat16 else [])
@@ -113,7 +185,7 @@ class Attention(Mixer):
         return [AttentionTiles()]
 
     # -- forward ------------------------------------------------------------
-    def forward(self, h, batch, cache, residual, rt) -> None:
+    def forward(self, h, batch, cache, residual, rt, accumulate=True) -> None:
         T = batch.T
         gb = batch.groups[cache.group]
         qkv = rt.rows("attention.qkv", self.q_dim + 2 * self.kv_dim, rt.dtype, T)
@@ -180,7 +252,7 @@ class Attention(Mixer):
             )
             K.attn_decode(q, cache.pool, o, items=tiles["decode_items"], n_items=n, part_o=part_o,
                           part_ml=part_ml, counters=counters, max_splits=max_splits, **common)
-        K.linear(o, self.params["wo"], residual, bias=self.params.get("bo"), accumulate=True)
+        K.linear(o, self.params["wo"], residual, bias=self.params.get("bo"), accumulate=accumulate, row_scale=self._scale)
 
 
 register_mixer("attention", Attention)

@@ -65,6 +65,9 @@ class ModelPlan:
     # checkpoint tensors (shell-style patterns) that files of this architecture may hold and the model
     # does not read: left-overs of the format such as tables that are recomputed
     ignorable_tensors: Tuple[str, ...] = ()
+    # copies of the residual stream a token's row holds, one behind the other (the embedding fills them all, the
+    # blocks' arrangement and the final norm know how to read them)
+    residual_streams: int = 1
 
     def describe(self) -> Dict[str, Any]:
         return {

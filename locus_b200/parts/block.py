@@ -7,6 +7,9 @@ float32 in every mode; the normed activations have the model's element type.
 ``OutputNorm``: x += norm1(mixer(x)); x += norm2(feed_forward(x)): the sublayers read x itself and the
 norms sit on what they give.
 
+``StreamedPreNorm``: pre-norm sublayers over several copies of the residual stream that are read as a weighted sum
+and mixed among themselves at every write-back (below).
+
 ``Embedding``: x = table[token] (llama.cpp:450).  ``LmHead``: logits = W . h in float32,
 W being the embedding table when the head is tied (llama.cpp:292-297, 512-513): the head then
 names the embedding's tensor as the source of its weight.
@@ -99,11 +102,108 @@ class OutputNorm(Arrangement):
         self.norm2.forward_add(y, x)
 
 
-class Embedding(Part):
-    def __init__(self, prefix: str, *, vocab: int, hidden: int, tensor: str = "") -> None:
-        """``tensor``: the checkpoint tensor's name where it is not ``<prefix>.weight``."""
+class StreamedPreNorm(Arrangement):
+    """Pre-norm sublayers over ``streams`` copies x_1 .. x_S of the residual stream (a row of x holds them one behind
+    the other).  For sublayer q (1: the mixer, 2: the feed-forward) with its own read weights a [S], write weights b
+    [S] and mixing matrix M [S, S] (indexed [from, to]):
+
+        u = sum_s a[s] x_s;   y = sublayer(norm_q(u));   x_t <- sum_s M[s, t] x_s + mult * b[t] * y   (all t at once).
+
+    ``streams`` = 0: one stream and no such tensors, x <- x + mult * sublayer(norm_q(x)).  ``feed_forward`` may be
+    absent (kind "none").  The sublayers write float32 rows; read, norm statistics and write-back are float32."""
+
+    def __init__(self, prefix: str, *, hidden: int, norm: PartSpec, mixer: PartSpec, feed_forward: PartSpec,
+                 streams: int = 0, mult: float = 1.0, mixer_prefix: str = "mix", ff_prefix: str = "mlp",
+                 norm1_name: str = "norm1", norm2_name: str = "norm2", bias_suffix: str = ".b",
+                 hc_names: tuple = ("hc1", "hc2")) -> None:
         super().__init__(prefix)
-        self.vocab, self.hidden = int(vocab), int(hidden)
+        self.hidden, self.mult = int(hidden), float(mult)
+        self.hyper = int(streams) > 0
+        self.S = max(int(streams), 1)
+        if self.S > K.MAX_STREAMS:
+            raise ValueError(f"streamed_pre_norm: {streams} streams exceed {K.MAX_STREAMS}")
+
+        def norm_part(name):
+            spec = PartSpec(norm.kind, {**norm.args, "streams": self.S, "tensor": f"{prefix}.{name}",
+                                        "bias_tensor": f"{prefix}.{name}{bias_suffix}"})
+            return make_part("norm", spec, f"{prefix}.{name}")
+
+        self.norm1 = norm_part(norm1_name)
+        self.mixer = make_part("mixer", mixer, f"{prefix}.{mixer_prefix}")
+        self.ff = None if feed_forward.kind == "none" else make_part("feed_forward", feed_forward, f"{prefix}.{ff_prefix}")
+        self.norm2 = norm_part(norm2_name) if self.ff is not None else None
+        self.hc_names = tuple(hc_names)[: 2 if self.ff is not None else 1]
+        self._coef = {}
+
+    def sub_parts(self):
+        return [self.norm1, self.mixer] + ([self.norm2, self.ff] if self.ff is not None else [])
+
+    def param_shapes(self):
+        if not self.hyper:
+            return {}
+        out = {}
+        for n in self.hc_names:
+            out.update({f"{n}.in": (self.S,), f"{n}.out": (self.S,), f"{n}.mix": (self.S, self.S)})
+        return out
+
+    def sources(self):
+        return [TensorSource(f"{self.prefix}.{name}", shape, name, 0, "norm" if name.endswith((".in", ".out")) else "bias")
+                for name, shape in self.param_shapes().items()]
+
+    def kernel_modules(self, dtype):
+        return ["elementwise"]
+
+    def bind(self, rt) -> None:
+        # the small tables as float32; the write weights carry the sublayers' common factor
+        self._coef = {}
+        for n in self.hc_names:
+            if self.hyper:
+                a = self.params[f"{n}.in"].float().contiguous()
+                b = (self.params[f"{n}.out"].float() * self.mult).contiguous()
+                m = self.params[f"{n}.mix"].float().contiguous()
+            else:
+                a = None
+                b = torch.full((1,), self.mult, dtype=torch.float32, device=rt.device)
+                m = torch.ones((1, 1), dtype=torch.float32, device=rt.device)
+            self._coef[n] = (a, b, m)
+
+    def _sublayer(self, which, norm, run, x, rt, T) -> None:
+        a, b, m = self._coef[which]
+        h = rt.rows("block.h", self.hidden, rt.dtype, T)
+        y = rt.rows("block.y", self.hidden, torch.float32, T)
+        norm.forward(x, h, coef=a)
+        run(h, y)
+        K.stream_update(x, y, m, b, self.S)
+
+    def forward(self, x, batch, cache, rt) -> None:
+        T = batch.T
+        rt.defer_add = False   # what a sublayer gives is written back here, at once: nothing may be left pending
+
+        def mixer(h, y):
+            if self.mixer.can_overwrite:
+                self.mixer.forward(h, batch, cache, y, rt, accumulate=False)
+            else:
+                y.zero_()
+                self.mixer.forward(h, batch, cache, y, rt)
+
+        def ff(h, y):
+            if self.ff.can_overwrite:
+                self.ff.forward(h, batch, y, rt, accumulate=False)
+            else:
+                y.zero_()
+                self.ff.forward(h, batch, y, rt)
+
+        self._sublayer(self.hc_names[0], self.norm1, mixer, x, rt, T)
+        if self.ff is not None:
+            self._sublayer(self.hc_names[1], self.norm2, ff, x, rt, T)
+
+
+class Embedding(Part):
+    def __init__(self, prefix: str, *, vocab: int, hidden: int, tensor: str = "", copies: int = 1) -> None:
+        """``tensor``: the checkpoint tensor's name where it is not ``<prefix>.weight``.  ``copies`` > 1: a row of the
+        output holds the embedding that many times (a model with several copies of the residual stream)."""
+        super().__init__(prefix)
+        self.vocab, self.hidden, self.copies = int(vocab), int(hidden), int(copies)
         self.tensor = str(tensor or prefix + ".weight")
 
     def param_shapes(self):
@@ -116,7 +216,10 @@ class Embedding(Part):
         return ["elementwise"]
 
     def forward(self, tokens: torch.Tensor, out: torch.Tensor) -> None:
-        K.embed_rows(tokens, self.params["table"], out)
+        if self.copies > 1:
+            K.embed_rows(tokens, self.params["table"], out, copies=self.copies)
+        else:
+            K.embed_rows(tokens, self.params["table"], out)
 
 
 class LmHead(Part):
@@ -143,5 +246,6 @@ class LmHead(Part):
 
 register_arrangement("pre_norm", PreNorm)
 register_arrangement("output_norm", OutputNorm)
+register_arrangement("streamed_pre_norm", StreamedPreNorm)
 register_embedding("embedding", Embedding)
 register_head("linear", LmHead)

@@ -102,21 +102,33 @@ class SparseMoe(FeedForward):
                  expert_intermediate: int, shared_intermediate: int = 0, shared_gate: bool = True,
                  weight_scale: float = 1.0, score_fn: str = "softmax", selection_bias: bool = False,
                  n_group: int = 1, n_group_used: int = 1, activation: str = "swiglu", router_bias: bool = False,
-                 names: Optional[dict] = None, shared_names: Optional[dict] = None) -> None:
+                 names: Optional[dict] = None, shared_names: Optional[dict] = None, n_identity: int = 0,
+                 group_score: str = "top2") -> None:
         """``router_bias``: the router has a bias [n_experts] that is part of its logits (selection and weights
         alike; with softmax scores and ``norm_topk`` the weights are then the softmax over the picked logits).
         ``names`` / ``shared_names``: tensor names where they differ from ``MOE_NAMES`` / ``DENSE_NAMES``.
         ``score_fn``: "softmax" over all experts or "sigmoid" of each router logit; ``selection_bias``:
         a float32 tensor ``<prefix>.gate.selection_bias`` [n_experts] is added to the scores for the
         selection only; ``n_group`` > 1: group-limited routing with ``n_group_used`` groups (the
-        parameters of the reference's ``moe_select``, src/locus/model/llama.cpp:900-980)."""
+        parameters of the reference's ``moe_select``, src/locus/model/llama.cpp:900-980); ``group_score``: what a group
+        is judged by, "top2" (the sum of its two best selection scores) or "best" (its best one).
+        ``n_identity``: the router has that many outputs more than there are experts with weights; they stand for
+        experts whose output is their input (times the weight).  Scores, selection bias, groups and top-k run over
+        all ``n_experts + n_identity`` router outputs."""
         super().__init__(prefix)
-        if not (1 <= top_k <= n_experts):
-            raise ValueError(f"sparse_moe: top_k {top_k} must be within 1..{n_experts}")
+        self.n_identity = int(n_identity)
+        if self.n_identity < 0:
+            raise ValueError(f"sparse_moe: {n_identity} identity experts")
+        self.R = int(n_experts) + self.n_identity        # the router's outputs
+        if not (1 <= top_k <= self.R):
+            raise ValueError(f"sparse_moe: top_k {top_k} must be within 1..{self.R}")
+        if group_score not in K.GROUP_SCORES:
+            raise ValueError(f"sparse_moe: group score {group_score!r} (known: {', '.join(K.GROUP_SCORES)})")
+        self.group_score = group_score
         if score_fn not in K.SCORE_FUNCTIONS:
             raise ValueError(f"sparse_moe: score function {score_fn!r} (known: {', '.join(K.SCORE_FUNCTIONS)})")
-        if not (1 <= n_group <= 32) or n_experts % n_group or not (1 <= n_group_used <= n_group):
-            raise ValueError(f"sparse_moe: {n_group} groups ({n_group_used} used) do not fit {n_experts} experts")
+        if not (1 <= n_group <= 32) or self.R % n_group or not (1 <= n_group_used <= n_group):
+            raise ValueError(f"sparse_moe: {n_group} groups ({n_group_used} used) do not fit {self.R} router outputs")
         self.score_fn, self.has_sel_bias = score_fn, bool(selection_bias)
         self.n_group, self.n_group_used = int(n_group), int(n_group_used)
         self.hidden, self.E, self.k = int(hidden), int(n_experts), int(top_k)
@@ -142,23 +154,23 @@ class SparseMoe(FeedForward):
 
     def param_shapes(self):
         s = {
-            "router": (self.E, self.hidden),
+            "router": (self.R, self.hidden),
             "up_exps": (self.E, self.I, self.hidden),
             "down_exps": (self.E, self.hidden, self.I),
         }
         if self.activation == "swiglu":
             s["gate_exps"] = (self.E, self.I, self.hidden)
         if self.has_router_bias:
-            s["router_bias"] = (self.E,)
+            s["router_bias"] = (self.R,)
         if self.shared_gate:
             s["shared_gate"] = (1, self.hidden)
         if self.has_sel_bias:
-            s["sel_bias"] = (self.E,)
+            s["sel_bias"] = (self.R,)
         return s
 
     def sources(self):
         p, n = self.prefix, self.names
-        out = [TensorSource(f"{p}.{n['router']}", (self.E, self.hidden), "router")]
+        out = [TensorSource(f"{p}.{n['router']}", (self.R, self.hidden), "router")]
         for e in range(self.E):
             if self.activation == "swiglu":
                 out.append(TensorSource(f"{p}.{n['expert_gate'].format(e=e)}", (self.I, self.hidden), "gate_exps", e * self.I))
@@ -166,11 +178,11 @@ class SparseMoe(FeedForward):
             out.append(TensorSource(f"{p}.{n['expert_down'].format(e=e)}", (self.hidden, self.I), "down_exps",
                                     e * self.hidden))
         if self.has_router_bias:
-            out.append(TensorSource(f"{p}.{n['router_bias']}", (self.E,), "router_bias", 0, "bias"))
+            out.append(TensorSource(f"{p}.{n['router_bias']}", (self.R,), "router_bias", 0, "bias"))
         if self.shared_gate:
             out.append(TensorSource(f"{p}.{n['shared_gate']}", (1, self.hidden), "shared_gate"))
         if self.has_sel_bias:
-            out.append(TensorSource(f"{p}.{n['selection_bias']}", (self.E,), "sel_bias", 0, "bias"))
+            out.append(TensorSource(f"{p}.{n['selection_bias']}", (self.R,), "sel_bias", 0, "bias"))
         return out
 
     def kernel_modules(self, dtype):
@@ -178,23 +190,25 @@ class SparseMoe(FeedForward):
 
     def bind(self, rt) -> None:
         self._layout = rt.shared_object(
-            ("expert_layout", self.E, self.k),
-            lambda: K.ExpertLayout(rt.max_tokens * self.k, self.E, 64, rt.device),
+            ("expert_layout", self.R, self.k),
+            lambda: K.ExpertLayout(rt.max_tokens * self.k, self.R, 64, rt.device),
         )
         self._scratch = rt.shared_object(
-            ("router_scratch", self.E + 1),
-            lambda: K.RouterScratch(rt.max_tokens, self.E + 1, rt.device),
+            ("router_scratch", self.R + 1),
+            lambda: K.RouterScratch(rt.max_tokens, self.R + 1, rt.device),
         )
         self._router_all = None
         bias = self.params.get("sel_bias")
         self._rule = dict(top_k=self.k, renorm=self.norm_topk, scale=self.weight_scale, score_fn=self.score_fn,
                           sel_bias=bias.float().contiguous() if bias is not None else None, n_group=self.n_group,
                           n_group_used=self.n_group_used)
+        if self.group_score != "top2":
+            self._rule["group_score"] = self.group_score
         # the router's own bias as float32 over the logit rows (the gate's row, when there is one, gets none)
         self._logit_bias = None
         if self.has_router_bias:
-            lb = torch.zeros(self.E + 1, dtype=torch.float32, device=rt.device)
-            lb[: self.E] = self.params["router_bias"].float()
+            lb = torch.zeros(self.R + 1, dtype=torch.float32, device=rt.device)
+            lb[: self.R] = self.params["router_bias"].float()
             self._logit_bias = lb
         r, g = self.params["router"], self.params.get("shared_gate")
         if (rt.dtype == torch.bfloat16 and r.dtype == torch.bfloat16 and self.hidden % 8 == 0
@@ -247,16 +261,16 @@ class SparseMoe(FeedForward):
                 shared_act = self.shared.forward_up(h, rt)
         if self._router_all is not None and K.USE_TENSOR_CORES:
             # bfloat16: router (and gate) logits on the tensor cores, one kernel for every batch shape
-            logits = self._scratch.logits.view(rt.max_tokens, self.E + 1)
-            if K.route_small_takes(T, self.k, self.E):
+            logits = self._scratch.logits.view(rt.max_tokens, self.R + 1)
+            if K.route_small_takes(T, self.k, self.R):
                 # a decode-sized batch: logits, selection and the expert layout in one launch
-                K.route_fused_small(h, self._router_all, logits, self.E, self.shared_gate, ids, wts, gamma, lay,
+                K.route_fused_small(h, self._router_all, logits, self.R, self.shared_gate, ids, wts, gamma, lay,
                                     self._scratch.fused_counter, n_tokens=T, tile_m=tile,
                                     logit_bias=self._logit_bias, **self._rule)
                 sorted_already = True
             else:
                 K.router_logits(h, self._router_all, logits, bias=self._logit_bias)
-                K.router_select(logits, self.E, self.shared_gate, ids, wts, gamma, n_tokens=T, **self._rule)
+                K.router_select(logits, self.R, self.shared_gate, ids, wts, gamma, n_tokens=T, **self._rule)
         else:
             K.router_topk(h, self.params["router"], self.params.get("shared_gate"), ids, wts, gamma,
                           scratch=self._scratch, logit_bias=self._logit_bias, **self._rule)
@@ -275,6 +289,13 @@ class SparseMoe(FeedForward):
             # the second product of the tensor-core path may walk the layout in larger tiles
             tile2 = K.expert_second_tile(n_pairs, self.E) if (all_bf16 and not streamed) else 0
             K.moe_sort(ids, n_pairs, lay, tile, tile2)
+        # the experts' weighted outputs, one row per (token, slot): in the model's element type (in bfloat16 a row is
+        # rounded once more, like every activation between kernels; their sum, the residual stream, stays float32)
+        pair_dt = torch.bfloat16 if (all_bf16 and rt.dtype == torch.bfloat16) else torch.float32
+        pair_out = rt.rows("moe.pair_out", self.hidden, pair_dt, n_pairs, per_token=self.k)
+        if self.n_identity:
+            # the picks without weights: their rows are the input itself, and the products below never see them
+            K.moe_identity(h, wts, lay, pair_out, n_pairs=n_pairs, top_k=self.k, n_real=self.E)
         if streamed or not all_bf16:
             # few rows per expert (or no tensor-core form): the kernels gather the token rows themselves
             self._first_product(h, act, x_rows=lay.sorted_pair, x_row_div=self.k, layout=lay, n_rows=n_pairs)
@@ -283,10 +304,6 @@ class SparseMoe(FeedForward):
             xs = rt.rows("moe.x_sorted", self.hidden, rt.dtype, n_pairs, per_token=self.k)
             K.gather_rows(h, lay.sorted_pair, self.k, xs, n_pairs)
             self._first_product(xs, act, layout=lay, n_rows=n_pairs)
-        # the experts' weighted outputs, one row per (token, slot): in the model's element type (in bfloat16 a row is
-        # rounded once more, like every activation between kernels; their sum, the residual stream, stays float32)
-        pair_dt = torch.bfloat16 if (all_bf16 and rt.dtype == torch.bfloat16) else torch.float32
-        pair_out = rt.rows("moe.pair_out", self.hidden, pair_dt, n_pairs, per_token=self.k)
         K.linear(act, self.params["down_exps"], pair_out, layout=lay, n_rows=n_pairs, row_scale=wts,
                  scale_rows=lay.sorted_pair, lists_ready=True, second_tiles=True)
         if overlap:

@@ -1,4 +1,5 @@
-"""RMSNorm(eps): out = x * rsqrt(mean(x^2) + eps) * w, statistics in float32.
+"""Norms.  RMSNorm(eps): out = x * rsqrt(mean(x^2) + eps) * w, statistics in float32.
+LayerNorm(eps): out = (x - mean) / sqrt(var + eps) * w + b (below).
 
 Formula and multiplication order of the reference's ``rmsnorm``
 (src/locus/backend/cpu_ops.cpp:1687-1699): no mean subtraction, no bias, the weight used
@@ -44,4 +45,36 @@ class RMSNorm(Norm):
         K.rmsnorm_add(y, self.params["weight"], self.eps, x)
 
 
+class LayerNorm(Norm):
+    """Layer norm with weight and bias, mean and variance (the mean of the squared deviations) in float32.  With
+    ``streams`` > 1 a row of x holds that many copies of the residual stream, one behind the other, and the norm
+    reads their weighted sum (``coef`` [streams] float32 on the device; None: the plain sum)."""
+
+    def __init__(self, prefix: str, *, width: int, eps: float, streams: int = 1, tensor: str = "",
+                 bias_tensor: str = "") -> None:
+        """``tensor`` / ``bias_tensor``: the checkpoint tensors' names where they are not ``<prefix>.weight`` and
+        ``<prefix>.bias``."""
+        super().__init__(prefix)
+        self.width, self.eps, self.streams = int(width), float(eps), int(streams)
+        self.tensor = str(tensor or prefix + ".weight")
+        self.bias_tensor = str(bias_tensor or prefix + ".bias")
+
+    def param_shapes(self):
+        return {"weight": (self.width,), "bias": (self.width,)}
+
+    def sources(self):
+        return [TensorSource(self.tensor, (self.width,), "weight", 0, "norm"),
+                TensorSource(self.bias_tensor, (self.width,), "bias", 0, "bias")]
+
+    def kernel_modules(self, dtype):
+        return ["elementwise"]
+
+    def forward(self, x: torch.Tensor, out: torch.Tensor, rows: Optional[torch.Tensor] = None, add=None,
+                coef: Optional[torch.Tensor] = None) -> None:
+        if add is not None:
+            add.apply(x)   # nothing is folded into this norm's pass
+        K.layernorm(x, self.params["weight"], self.params["bias"], self.eps, out, rows, n_streams=self.streams, coef=coef)
+
+
 register_norm("rmsnorm", RMSNorm)
+register_norm("layernorm", LayerNorm)

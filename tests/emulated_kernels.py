@@ -20,8 +20,8 @@ def _f(t: torch.Tensor) -> torch.Tensor:
     return t.to(torch.float64 if PRECISE else torch.float32)
 
 
-def embed_rows(tokens, table, out):
-    out.copy_(table[tokens.long()].to(out.dtype))
+def embed_rows(tokens, table, out, copies=1):
+    out.copy_(table[tokens.long()].to(out.dtype).repeat(1, copies))
 
 
 def attn_chunk_tc_takes(q, head_dim, page_tokens, n_tokens, max_ctx=0):
@@ -66,7 +66,7 @@ def linear(x, w, out, *, w2=None, bias=None, accumulate=False, row_scale=None, s
     else:
         y = torch.zeros(M, w.shape[1], dtype=xin.dtype)
         off = layout.offsets.tolist()
-        for e in range(layout.n_experts):
+        for e in range(w.shape[0]):   # experts behind the weights have none: their rows are not this product's
             a, b = off[e], off[e + 1]
             if b > a:
                 ye = xin[a:b] @ _f(w[e]).T
@@ -80,6 +80,9 @@ def linear(x, w, out, *, w2=None, bias=None, accumulate=False, row_scale=None, s
     if row_scale is not None:
         rs = row_scale[scale_rows[:M].long()] if scale_rows is not None else row_scale[:M]
         y = y * _f(rs)[:, None]
+    if layout is not None:
+        M = min(M, int(layout.offsets[w.shape[0]]))   # a grouped product writes the rows of its experts only
+        y = y[:M]
     if accumulate:
         out[:M] += y.to(out.dtype)
     else:
@@ -165,7 +168,7 @@ def attn_decode(q, pool, out, *, seg_q0, seg_qn, seg_ctx, block_table, items, n_
           scale=scale)
 
 
-def _select(logits_row, top_k, renorm, scale, score_fn, sel_bias, n_group, n_group_used):
+def _select(logits_row, top_k, renorm, scale, score_fn, sel_bias, n_group, n_group_used, group_score="top2"):
     """The selection rule of csrc/moe_route.cu (select_token) for one token."""
     E = logits_row.shape[0]
     r = logits_row
@@ -181,7 +184,7 @@ def _select(logits_row, top_k, renorm, scale, score_fn, sel_bias, n_group, n_gro
         gs = []
         for g in range(n_group):
             top2 = torch.sort(torch.cat([sel[g * per : (g + 1) * per], torch.full((2,), -1e30, dtype=sel.dtype)]), descending=True).values
-            gs.append(float(top2[0]) + (float(top2[1]) if per > 1 else 0.0))
+            gs.append(float(top2[0]) + (float(top2[1]) if per > 1 and group_score == "top2" else 0.0))
         keep = []
         for _ in range(n_group_used):
             keep.append(max((g for g in range(n_group) if g not in keep), key=lambda g: (gs[g], -g)))
@@ -197,13 +200,13 @@ def _select(logits_row, top_k, renorm, scale, score_fn, sel_bias, n_group, n_gro
 
 
 def router_topk(h, w_router, w_gate, ids, wts, gamma, *, top_k, renorm, scale=1.0, scratch=None, score_fn="softmax",
-                sel_bias=None, n_group=1, n_group_used=1, logit_bias=None):
+                sel_bias=None, n_group=1, n_group_used=1, logit_bias=None, group_score="top2"):
     T = h.shape[0]
     r = _f(h) @ _f(w_router).T
     if logit_bias is not None:
         r = r + _f(logit_bias[: r.shape[1]])
     for t in range(T):
-        picked, w = _select(r[t], top_k, renorm, scale, score_fn, sel_bias, n_group, n_group_used)
+        picked, w = _select(r[t], top_k, renorm, scale, score_fn, sel_bias, n_group, n_group_used, group_score)
         for j, e in enumerate(picked):
             ids[t * top_k + j] = e
             wts[t * top_k + j] = w[j]
@@ -221,10 +224,10 @@ def router_logits(h, w_all, logits, bias=None):
 
 
 def router_select(logits, n_experts, has_gate, ids, wts, gamma, *, n_tokens, top_k, renorm, scale=1.0,
-                  score_fn="softmax", sel_bias=None, n_group=1, n_group_used=1):
+                  score_fn="softmax", sel_bias=None, n_group=1, n_group_used=1, group_score="top2"):
     lg = _f(logits[:n_tokens, :n_experts])
     for t in range(n_tokens):
-        picked, w = _select(lg[t], top_k, renorm, scale, score_fn, sel_bias, n_group, n_group_used)
+        picked, w = _select(lg[t], top_k, renorm, scale, score_fn, sel_bias, n_group, n_group_used, group_score)
         for j, e in enumerate(picked):
             ids[t * top_k + j] = e
             wts[t * top_k + j] = w[j]
@@ -453,6 +456,111 @@ def retention_gate_norm(o_raw, qkvg, gate_offset, eps, out, *, n_heads, v_dim):
     out[:T] = (unit * (g / (1.0 + torch.exp(-g)))).reshape(T, -1).to(out.dtype)
 
 
+def layernorm(x, w, b, eps, out, rows=None, n_streams=1, coef=None):
+    n, H = out.shape
+    xs = _f(x if rows is None else x[rows.long()])[:n].view(n, n_streams, H)
+    c = _f(coef) if coef is not None else torch.ones(n_streams, dtype=xs.dtype)
+    u = (xs * c[None, :, None]).sum(1)
+    d = u - u.mean(-1, keepdim=True)
+    out.copy_((d / torch.sqrt((d * d).mean(-1, keepdim=True) + eps) * _f(w) + _f(b)).to(out.dtype))
+
+
+def stream_update(x, y, mix, out_coef, n_streams):
+    n, H = y.shape
+    old = _f(x[:n]).view(n, n_streams, H)
+    new = torch.einsum("st,nsh->nth", _f(mix), old) + _f(out_coef)[None, :, None] * _f(y)[:, None, :]
+    x[:n] = new.reshape(n, n_streams * H).to(x.dtype)
+
+
+def moe_identity(h, wts, layout, pair_out, *, n_pairs, top_k, n_real):
+    first = int(layout.offsets[n_real])
+    for r in range(first, n_pairs):
+        pair = int(layout.sorted_pair[r])
+        pair_out[r] = (_f(wts[pair]) * _f(h[pair // top_k])).to(pair_out.dtype)
+    for te, nt in ((layout.tile_expert, layout.n_tiles), (layout.tile2_expert, layout.n_tiles2)):
+        if te is layout.tile2_expert and not layout.tile2_m:
+            continue
+        n = int(nt[0])
+        cut = [i for i in range(n) if int(te[i]) >= n_real]
+        if cut:
+            nt[0] = cut[0]
+
+
+def gated_recurrence(q, off_q, k, off_k, v, off_v, keep, take, state, state_offset, state_slots, seg_q0, seg_qn, n_seg,
+                     out, *, n_heads, heads_per_group, dim, v_dim, ones=False, q_scale=1.0, short=True, long=True,
+                     longest_new=0):
+    H, d, dv = n_heads, dim, v_dim
+    dvx = dv + (1 if ones else 0)
+    G = H // heads_per_group
+    grp = torch.arange(H) // heads_per_group
+    for seg in range(n_seg):
+        q0, qn, slot = int(seg_q0[seg]), int(seg_qn[seg]), int(state_slots[seg])
+        S = _f(state[slot, state_offset:state_offset + H * d * dvx]).view(H, d, dvx).clone()
+        for t in range(q0, q0 + qn):
+            qq = _f(q[t, off_q:off_q + G * d]).view(G, d)[grp] * q_scale
+            kk = _f(k[t, off_k:off_k + G * d]).view(G, d)[grp]
+            vv = _f(v[t, off_v:off_v + H * dv]).view(H, dv)
+            if ones:
+                vv = torch.cat([vv, torch.ones(H, 1, dtype=vv.dtype)], 1)
+            S = _f(keep[t]).view(H, 1, 1) * S + (_f(take[t]).view(H, 1) * kk)[:, :, None] * vv[:, None, :]
+            out[t] = torch.einsum("hdv,hd->hv", S, qq).reshape(-1).to(out.dtype)
+        state[slot, state_offset:state_offset + H * d * dvx] = S.reshape(-1).to(state.dtype)
+
+
+def mlstm_gates(proj, off_i, off_f, cap, state, m_offset, state_slots, seg_q0, seg_qn, n_seg, keep, take, m_out, *, n_heads):
+    H = n_heads
+    for seg in range(n_seg):
+        q0, qn, slot = int(seg_q0[seg]), int(seg_qn[seg]), int(state_slots[seg])
+        m = _f(state[slot, m_offset:m_offset + H]).clone()
+        for t in range(q0, q0 + qn):
+            i = cap * torch.tanh(_f(proj[t, off_i:off_i + H]) / cap)
+            f = torch.nn.functional.logsigmoid(cap * torch.tanh(_f(proj[t, off_f:off_f + H]) / cap))
+            m_new = torch.maximum(f + m, i)
+            keep[t] = torch.exp(f + m - m_new).to(keep.dtype)
+            take[t] = torch.exp(i - m_new).to(take.dtype)
+            m_out[t] = m_new.to(m_out.dtype)
+            m = m_new
+        state[slot, m_offset:m_offset + H] = m.to(state.dtype)
+
+
+def mlstm_out(o_raw, m_t, proj, off_g, w, eps, out, *, n_heads, v_dim):
+    T, H, dv = out.shape[0], n_heads, v_dim
+    o = _f(o_raw[:T]).view(T, H, dv + 1)
+    den = torch.maximum(o[..., dv].abs(), torch.exp(-_f(m_t[:T]))) + 1e-6
+    u = o[..., :dv] / den[..., None]
+    u = u / torch.sqrt((u * u).mean(-1, keepdim=True) + eps)
+    g = _f(proj[:T, off_g:off_g + H * dv])
+    out[:T] = (u.reshape(T, H * dv) * _f(w) * torch.sigmoid(g)).to(out.dtype)
+
+
+def ssm_conv(proj, off_xbc, off_dt, conv_w, conv_b, dt_bias, a_log, state, conv_offset, state_slots, seg_q0, seg_qn, n_seg,
+             act, keep, take, *, n_heads, longest_new=0):
+    C, taps = conv_w.shape
+    H = n_heads
+    for seg in range(n_seg):
+        q0, qn, slot = int(seg_q0[seg]), int(seg_qn[seg]), int(state_slots[seg])
+        old = _f(state[slot, conv_offset:conv_offset + C * (taps - 1)]).view(C, taps - 1)
+        xin = torch.cat([old.T, _f(proj[q0:q0 + qn, off_xbc:off_xbc + C])], 0)      # [taps - 1 + qn, C]
+        acc = _f(conv_b)[None, :].repeat(qn, 1)
+        for j in range(taps):
+            acc = acc + xin[j:j + qn] * _f(conv_w)[:, j]
+        act[q0:q0 + qn] = (acc / (1.0 + torch.exp(-acc))).to(act.dtype)
+        state[slot, conv_offset:conv_offset + C * (taps - 1)] = xin[qn:].T.reshape(-1).to(state.dtype)
+        dt = torch.nn.functional.softplus(_f(proj[q0:q0 + qn, off_dt:off_dt + H]) + _f(dt_bias))
+        keep[q0:q0 + qn] = torch.exp(-torch.exp(_f(a_log)) * dt).to(keep.dtype)
+        take[q0:q0 + qn] = dt.to(take.dtype)
+
+
+def ssm_out(y, act, proj, off_z, d_skip, w, eps, out, *, parts, v_dim):
+    T, inner = out.shape
+    x = _f(act[:T, :inner])
+    z = _f(proj[:T, off_z:off_z + inner])
+    u = (_f(y[:T]) + _f(d_skip).repeat_interleave(v_dim)[None, :] * x) * (z / (1.0 + torch.exp(-z)))
+    u = u.view(T, parts, inner // parts)
+    u = u / torch.sqrt((u * u).mean(-1, keepdim=True) + eps)
+    out[:T] = (u.reshape(T, inner) * _f(w)).to(out.dtype)
+
+
 def head_tile(n_tokens, dtype, widths_ok):
     return 8 if (widths_ok and n_tokens <= 8) else 64
 
@@ -460,7 +568,8 @@ def head_tile(n_tokens, dtype, widths_ok):
 _NAMES = ["embed_rows", "rmsnorm", "rmsnorm_adds", "attn_chunk_tc_takes", "linear", "rope_kv_write", "attn_chunk", "attn_chunk_mma", "attn_decode", "router_topk", "router_logits", "router_select",
           "moe_sort", "route_small", "route_small_takes", "route_fused_small", "moe_combine", "gather_rows", "apply_penalties", "sample",
           "cast_rows", "rmsnorm_add", "latent_prep", "latent_q_split", "latent_attn", "heads_to_rows", "retention_scan",
-          "retention_gate_norm", "head_tile", "latent_attn_mma_takes"]
+          "retention_gate_norm", "head_tile", "latent_attn_mma_takes", "layernorm", "stream_update", "moe_identity",
+          "gated_recurrence", "mlstm_gates", "mlstm_out", "ssm_conv", "ssm_out"]
 
 
 def install(monkeypatch) -> None:
