@@ -150,8 +150,9 @@ def gated_expert(weights, p: str, h: torch.Tensor) -> torch.Tensor:
     return (silu(h @ _w(weights, p + ".gate").T) * (h @ _w(weights, p + ".up").T)) @ _w(weights, p + ".down").T
 
 
-def route(weights, p: str, f: dict, h: torch.Tensor, picks: Optional[List[List[int]]] = None):
-    """(picked outputs [T, top], weights [T, top]).  ``picks``: use these picks instead of choosing."""
+def route(weights, p: str, f: dict, h: torch.Tensor, picks: Optional[List[List[int]]] = None, aux: Optional[dict] = None):
+    """(picked experts [T, top], weights [T, top]).  ``picks``: use these picks instead of choosing.  ``aux``: gets the
+    choice scores, the groups' scores and the choice scores with the closed groups at minus infinity."""
     r = f["router"]
     E, I, top = int(r["experts"]), int(r.get("identity", 0)), int(r["top"])
     groups = r.get("groups") or {"count": 1, "keep": 1}
@@ -163,15 +164,17 @@ def route(weights, p: str, f: dict, h: torch.Tensor, picks: Optional[List[List[i
     open_ = torch.zeros_like(best, dtype=torch.bool).scatter_(1, kept, True).repeat_interleave(per, 1)
     masked = torch.where(open_, choice, torch.full_like(choice, -math.inf))
     ids = torch.topk(masked, top, -1).indices
+    if aux is not None:
+        aux.update(choice=choice, groups=best, masked=masked, own=ids)
     if picks is not None:
         ids = torch.tensor(picks, dtype=torch.long)
     w = torch.gather(s, 1, ids)
     return ids, w / (w.sum(-1, keepdim=True) + 1e-20)
 
 
-def moe_ff(weights, p: str, f: dict, h: torch.Tensor, picks=None) -> torch.Tensor:
+def moe_ff(weights, p: str, f: dict, h: torch.Tensor, picks=None, aux=None) -> torch.Tensor:
     E = int(f["router"]["experts"])
-    ids, w = route(weights, p, f, h, picks)
+    ids, w = route(weights, p, f, h, picks, aux)
     out = torch.zeros_like(h)
     for t in range(h.shape[0]):
         for e, g in zip(ids[t].tolist(), w[t]):
@@ -195,8 +198,10 @@ def run_order(cfg: dict) -> List[int]:
 
 
 def forward(weights: Dict[str, torch.Tensor], cfg: dict, tokens, picks: Optional[dict] = None,
-            layers_out: Optional[list] = None) -> torch.Tensor:
-    """Logits [T, vocab] of one sequence from its first token.  ``picks`` {(call index, row): experts}."""
+            layers_out: Optional[list] = None, aux: Optional[dict] = None) -> torch.Tensor:
+    """Logits [T, vocab] of one sequence from its first token.  ``picks`` {index in the run order: experts of every
+    row}; ``aux`` gets {index in the run order: the router's scores} (see ``route``); ``layers_out`` the sum of the
+    streams behind every layer run."""
     eps, mult = float(cfg["norm"]["eps"]), float(cfg.get("residual_mult", 1.0))
     n_streams = int(cfg.get("streams", 0))
     x0 = _w(weights, "embed")[torch.as_tensor(tokens, dtype=torch.long)]
@@ -223,7 +228,8 @@ def forward(weights: Dict[str, torch.Tensor], cfg: dict, tokens, picks: Optional
             raise ValueError(layer["type"])
         if layer.get("mlp"):
             pk = None if picks is None else picks.get(call)
-            sublayer(2, p, lambda h: moe_ff(weights, p + ".mlp", layer["mlp"], h, pk))
+            ax = None if aux is None else aux.setdefault(call, {})
+            sublayer(2, p, lambda h: moe_ff(weights, p + ".mlp", layer["mlp"], h, pk, ax))
         if layers_out is not None:
             layers_out.append(sum(xs))
     x = sum(xs)
