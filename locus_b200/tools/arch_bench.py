@@ -1,12 +1,15 @@
-"""Prefill and decode throughput of the Lalepel design at layer sizes that resemble a real model's, beside the
-Qwen2-MoE architecture at equal sizes (random weights, synthetic token ids, one GPU).
+"""Prefill and decode throughput of the Lalepel or the Pozozen design at layer sizes that resemble a real model's,
+beside the Qwen2-MoE architecture at equal sizes (random weights, synthetic token ids, one GPU).
 
-    python -m locus_b200.tools.arch_bench [--size m|s] [--layers 4] [--prefill 2048] [--batch 8] [--context 4096]
-                                          [--steps 16] [--warmup 3] [--dtype bf16|fp32] [--kernels]
+    python -m locus_b200.tools.arch_bench [--design lalepel|pozozen] [--size m|s] [--layers 4] [--prefill 2048]
+                                          [--batch 8] [--context 4096] [--steps 16] [--warmup 3] [--dtype bf16|fp32]
+                                          [--kernels]
 
 Both models get the same width, head count and head sizes, experts, picks per token, expert and shared widths and
 vocabulary; Lalepel's layers cycle through (latent attention, latent attention, retention, latent attention), all
-with routed experts.  Timed on the device with CUDA events after warm-up; every step reads its weights (several
+with routed experts; Pozozen's through (attention beside a state-space mixer, matrix memory, matrix memory, attention
+beside a state-space mixer) over two copies of the residual stream, with four identity experts beside the routed ones
+in eight (or four) groups of which half stay open.  Timed on the device with CUDA events after warm-up; every step reads its weights (several
 hundred MB: more than the L2 holds).  ``--kernels`` adds, for one eager prefill step and one eager decode step of
 each model, the time by kernel entry point, and for the mixers' own kernels what their bytes or flops would take
 at the measured peaks.  Prints one JSON line.
@@ -21,9 +24,9 @@ import sys
 SIZES = {
     # width, heads, head size (Qwen) = unrotated + rotated (Lalepel), value size, ranks, experts
     "m": dict(width=2048, heads=16, dim=128, rot=64, vdim=128, q_rank=768, kv_rank=512, window=4096, experts=60, top=4,
-              ff=1408, shared=5632, vocab=151936, ret_dim=128),
+              ff=1408, shared=5632, vocab=151936, ret_dim=128, ssm_vdim=64, ssm_state=128),
     "s": dict(width=1024, heads=8, dim=64, rot=32, vdim=64, q_rank=384, kv_rank=256, window=1024, experts=32, top=2,
-              ff=704, shared=2816, vocab=32000, ret_dim=64),
+              ff=704, shared=2816, vocab=32000, ret_dim=64, ssm_vdim=64, ssm_state=64),
 }
 
 
@@ -39,6 +42,23 @@ def lalepel_config(z, n_layers):
         "decay": [1.0 - 2.0 ** (-5 - 0.5 * i) for i in range(z["heads"])]}}
     return {"architecture": "Lalepel", "width": z["width"], "vocab": z["vocab"], "norm": {"eps": 1e-6},
             "layers": [(ret if i % 4 == 2 else lat) for i in range(n_layers)]}
+
+
+def pozozen_config(z, n_layers):
+    ident = 4
+    count = 8 if (z["experts"] + ident) % 8 == 0 else 4
+    moe = {"kind": "moe", "router": {"experts": z["experts"], "top": z["top"], "identity": ident,
+                                     "groups": {"count": count, "keep": count // 2}},
+           "expert": {"ff": z["ff"]}, "shared": {"ff": z["shared"]}}
+    par = {"type": "parallel", "mlp": moe, "mixer": {
+        "left": {"heads": z["heads"], "kv_heads": z["heads"], "dim": z["dim"], "vdim": z["vdim"], "scale": z["dim"] ** -0.5,
+                 "mask": {"size": z["window"]}},
+        "right": {"heads": 2 * z["width"] // z["ssm_vdim"], "vdim": z["ssm_vdim"], "state": z["ssm_state"], "groups": 1,
+                  "conv": 4, "norm_groups": 1},
+        "left_scale": 0.5, "right_scale": 0.5}}
+    mem = {"type": "mlstm", "mlp": moe, "mixer": {"heads": z["heads"], "dim": z["ret_dim"], "vdim": z["vdim"], "gate_cap": 15.0}}
+    return {"architecture": "Pozozen", "width": z["width"], "vocab": z["vocab"], "norm": {"eps": 1e-6}, "residual_mult": 0.5,
+            "streams": 2, "layers": [(mem if i % 4 in (1, 2) else par) for i in range(n_layers)]}
 
 
 def qwen_config(z, n_layers, max_pos):
@@ -82,7 +102,9 @@ def run(args) -> dict:
     W, steps = max(3, args.warmup), args.steps
     pk = peaks()
     gen = torch.Generator().manual_seed(5)
-    raws = {"lalepel": lalepel_config(z, args.layers), "qwen2_moe": qwen_config(z, args.layers, max(ctx, T) + 8)}
+    design = args.design
+    own = lalepel_config(z, args.layers) if design == "lalepel" else pozozen_config(z, args.layers)
+    raws = {design: own, "qwen2_moe": qwen_config(z, args.layers, max(ctx, T) + 8)}
     raws["qwen2_moe"].pop("_head")
     out = {}
     for name, raw in raws.items():
@@ -163,6 +185,31 @@ def run(args) -> dict:
     # what the mixers' own kernels have to do per layer, at the measured peaks
     H, R = z["heads"], z["kv_rank"] + z["rot"]
     keys_avg = sum(min(p + 1, z["window"]) for p in range(T)) / T
+    fma_tflops = 148 * 128 * 2 * 1.965e9 / 1e12       # float32 FMAs of the CUDA cores at the top clock
+    if design == "pozozen":
+        sh, sdv, sn = 2 * z["width"] // z["ssm_vdim"], z["ssm_vdim"], z["ssm_state"]
+
+        def chunk_flops(heads, d, dvx):
+            # per token and head: its row of Q K^T and of (Q K^T * D) V within a chunk of 32, Q S, and the state's update
+            return 2.0 * T * heads * (32 * d + 32 * dvx + 2 * d * dvx)
+
+        win_keys = sum(min(p + 1, z["window"]) for p in range(T)) / T
+        bounds = {
+            "attn_prefill_us": 2.0 * T * win_keys * H * 2 * z["dim"] / (pk["bf16_tflops"] * 1e12) * 1e6,
+            "attn_decode_us": B * min(ctx, z["window"]) * 2 * H * z["dim"] * el / (pk["hbm_gbs"] * 1e9) * 1e6,
+            "ssm_recurrence_prefill_us": chunk_flops(sh, sn, sdv) / (fma_tflops * 1e12) * 1e6,
+            "ssm_recurrence_decode_us": B * sh * sn * sdv * 4 * 2 / (pk["hbm_gbs"] * 1e9) * 1e6,
+            "mlstm_recurrence_prefill_us": chunk_flops(H, z["ret_dim"], z["vdim"] + 1) / (fma_tflops * 1e12) * 1e6,
+            "mlstm_recurrence_decode_us": B * H * z["ret_dim"] * (z["vdim"] + 1) * 4 * 2 / (pk["hbm_gbs"] * 1e9) * 1e6,
+            "qwen_attn_prefill_us": 2.0 * T * (T + 1) / 2 * H * 2 * z["dim"] / (pk["bf16_tflops"] * 1e12) * 1e6,
+            "qwen_attn_decode_us": B * ctx * 2 * H * z["dim"] * el / (pk["hbm_gbs"] * 1e9) * 1e6,
+            "fp32_fma_tflops": fma_tflops,
+        }
+        return {"metric": f"prefill and decode tokens/s, Pozozen beside Qwen2-MoE at equal layer sizes ({args.size}, "
+                          f"{args.layers} layers, {args.dtype})",
+                "size": z, "layers": args.layers, "dtype": args.dtype, "data": "synthetic", "designs": out,
+                "bounds_per_layer": bounds, "peaks": pk,
+                "l2": "no flush: every step reads its weights, more than the 126 MB L2"}
     bounds = {
         "latent_attn_prefill_us": 2.0 * T * keys_avg * H * (R + z["kv_rank"]) / (pk["bf16_tflops"] * 1e12) * 1e6,
         "qwen_attn_prefill_us": 2.0 * T * (T + 1) / 2 * H * 2 * z["dim"] / (pk["bf16_tflops"] * 1e12) * 1e6,
@@ -180,6 +227,7 @@ def run(args) -> dict:
 
 def main(argv=None) -> int:
     ap = argparse.ArgumentParser(prog="arch_bench", description=__doc__.split("\n\n")[0])
+    ap.add_argument("--design", default="lalepel", choices=["lalepel", "pozozen"])
     ap.add_argument("--size", default="m", choices=sorted(SIZES))
     ap.add_argument("--layers", type=int, default=4)
     ap.add_argument("--prefill", type=int, default=2048)
