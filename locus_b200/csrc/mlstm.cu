@@ -13,45 +13,54 @@
 
 __device__ __forceinline__ float log_sigmoid(float x) { return fminf(x, 0.f) - log1pf(expf(-fabsf(x))); }
 
-// One block per (head, segment): the pre-activations are turned into i and f by all threads, one thread walks the
-// running maximum (additions and maxima only), all threads form keep and take.
+// One block per (head, segment), a tile of MG_TILE tokens at a time through shared memory: the pre-activations are
+// turned into i and f by all threads, one thread walks the running maximum (additions and maxima only, operands in
+// shared memory), all threads form keep and take.
+#define MG_TILE 1024
+
 __global__ void __launch_bounds__(256) mlstm_gates_kernel(const float* __restrict__ proj, int ld, int off_i, int off_f,
                                                           float cap, float* __restrict__ m_state, long long slot_stride,
                                                           const int* __restrict__ state_slots,
                                                           const int* __restrict__ seg_q0, const int* __restrict__ seg_qn,
                                                           float* __restrict__ keep, float* __restrict__ take,
                                                           float* __restrict__ m_out, int H) {
+    __shared__ float s_i[MG_TILE], s_f[MG_TILE], s_m[MG_TILE + 1];
     pdl_entry();
     pdl_trigger();
     const int h = blockIdx.x, seg = blockIdx.y;
     const int q0 = seg_q0[seg], qn = seg_qn[seg];
     float* mp = m_state + static_cast<size_t>(state_slots[seg]) * slot_stride + h;
-    for (int t = threadIdx.x; t < qn; t += blockDim.x) {
-        const size_t row = static_cast<size_t>(q0 + t);
-        const float zi = proj[row * ld + off_i + h], zf = proj[row * ld + off_f + h];
-        take[row * H + h] = cap * tanhf(zi / cap);
-        keep[row * H + h] = log_sigmoid(cap * tanhf(zf / cap));
-    }
-    __syncthreads();
-    if (threadIdx.x == 0) {
-        float m = *mp;
-        for (int t = 0; t < qn; ++t) {
-            const size_t at = static_cast<size_t>(q0 + t) * H + h;
-            m = fmaxf(keep[at] + m, take[at]);
+    if (threadIdx.x == 0) s_m[0] = *mp;
+    for (int t0 = 0; t0 < qn; t0 += MG_TILE) {
+        const int n = min(MG_TILE, qn - t0);
+        for (int t = threadIdx.x; t < n; t += blockDim.x) {
+            const size_t row = static_cast<size_t>(q0 + t0 + t);
+            const float zi = proj[row * ld + off_i + h], zf = proj[row * ld + off_f + h];
+            s_i[t] = cap * tanhf(zi / cap);
+            s_f[t] = log_sigmoid(cap * tanhf(zf / cap));
+        }
+        __syncthreads();
+        if (threadIdx.x == 0) {
+            float m = s_m[0];   // the maximum behind the tile before (or the slot's)
+#pragma unroll 8
+            for (int t = 0; t < n; ++t) {
+                m = fmaxf(s_f[t] + m, s_i[t]);
+                s_m[t + 1] = m;
+            }
+        }
+        __syncthreads();
+        for (int t = threadIdx.x; t < n; t += blockDim.x) {
+            const size_t at = static_cast<size_t>(q0 + t0 + t) * H + h;
+            const float m_prev = s_m[t], m = s_m[t + 1];
+            keep[at] = expf(s_f[t] + m_prev - m);
+            take[at] = expf(s_i[t] - m);
             m_out[at] = m;
         }
+        __syncthreads();
+        if (threadIdx.x == 0) s_m[0] = s_m[n];
+        __syncthreads();
     }
-    __syncthreads();
-    const float m_first = *mp;
-    for (int t = threadIdx.x; t < qn; t += blockDim.x) {
-        const size_t at = static_cast<size_t>(q0 + t) * H + h;
-        const float m_prev = t > 0 ? m_out[at - H] : m_first, m = m_out[at];
-        const float f = keep[at], i = take[at];
-        keep[at] = expf(f + m_prev - m);
-        take[at] = expf(i - m);
-    }
-    __syncthreads();
-    if (threadIdx.x == 0 && qn > 0) *mp = m_out[static_cast<size_t>(q0 + qn - 1) * H + h];
+    if (threadIdx.x == 0 && qn > 0) *mp = s_m[0];
 }
 
 // proj [T, ld] float32; m_state: the address of head 0's m in slot 0 (slots are slot_stride floats apart);

@@ -229,8 +229,8 @@ __global__ void __launch_bounds__(256) gated_inter_kernel(const RecArgs a, int c
     float* Ks = Qs + REC_CHUNK * ldq;          // [C][ldq]
     float* Vs = Ks + REC_CHUNK * ldq;          // [C][cols]
     float* Ss = Vs + REC_CHUNK * cols;         // [d4][cols]
-    float* cum = Ss + d4 * cols;               // [C] keeps multiplied up to and with token i
-    float* wj = cum + REC_CHUNK;               // [C] take_j times the keeps behind j
+    float* kp = Ss + d4 * cols;                // [C] the chunk's keeps (1 behind its end)
+    float* tk = kp + REC_CHUNK;                // [C] and takes (0 behind its end)
     const int tid = threadIdx.x, lane = tid & 31, wid = tid >> 5;
     const int c = lane % cols, sub = lane / cols, nsub = 32 / cols;
     float* S = a.state + static_cast<size_t>(a.state_slots[seg]) * a.slot_stride + static_cast<size_t>(h) * d * dvx;
@@ -259,19 +259,23 @@ __global__ void __launch_bounds__(256) gated_inter_kernel(const RecArgs a, int c
             if (j < n) v = c0 + cc < dv ? a.v[static_cast<size_t>(q0 + t0 + j) * a.ldv + off_v + c0 + cc] : (c0 + cc < dvx ? 1.0f : 0.f);
             Vs[i] = v;
         }
-        if (tid == 0) {
-            float p = 1.f;
-            for (int j = 0; j < n; ++j) {
-                p *= a.keep[static_cast<size_t>(q0 + t0 + j) * a.H + h];
-                cum[j] = p;
-            }
-            p = 1.f;
-            for (int j = n - 1; j >= 0; --j) {
-                wj[j] = p * a.take[static_cast<size_t>(q0 + t0 + j) * a.H + h];
-                p *= a.keep[static_cast<size_t>(q0 + t0 + j) * a.H + h];
-            }
+        if (tid < REC_CHUNK) {
+            kp[tid] = tid < n ? a.keep[static_cast<size_t>(q0 + t0 + tid) * a.H + h] : 1.f;
+            tk[tid] = tid < n ? a.take[static_cast<size_t>(q0 + t0 + tid) * a.H + h] : 0.f;
         }
         __syncthreads();
+        // Every warp forms the products of the keeps for itself, lane j those of token j: cum = keep_0 .. keep_j, and
+        // w = take_j times the keeps behind j (two scans by shuffles; no warp waits for another).
+        float cum = kp[lane], suf = kp[lane];
+#pragma unroll
+        for (int o = 1; o < 32; o <<= 1) {
+            const float up = __shfl_up_sync(0xffffffffu, cum, o), dn = __shfl_down_sync(0xffffffffu, suf, o);
+            if (lane >= o) cum *= up;
+            if (lane + o < 32) suf *= dn;
+        }
+        const float behind = __shfl_down_sync(0xffffffffu, suf, 1);
+        const float w_lane = tk[lane] * (lane < 31 ? behind : 1.f);
+        const float cum_last = __shfl_sync(0xffffffffu, cum, n - 1);
         {   // o += c_i Q S: rows i = wid + 8 u, column c; the lanes' shares of the rows of S are summed by shuffles
             float inter[4] = {0.f, 0.f, 0.f, 0.f};
             for (int r4 = sub; r4 < d4 / 4; r4 += nsub) {
@@ -290,9 +294,10 @@ __global__ void __launch_bounds__(256) gated_inter_kernel(const RecArgs a, int c
             for (int u = 0; u < 4; ++u) {
                 for (int o = cols; o < 32; o <<= 1) inter[u] += __shfl_xor_sync(0xffffffffu, inter[u], o);
                 const int i = wid + 8 * u;
+                const float ci = __shfl_sync(0xffffffffu, cum, i);
                 if (sub == 0 && i < n && c0 + c < dvx) {
                     float* dst = a.out + static_cast<size_t>(q0 + t0 + i) * a.ldo + h * dvx + c0 + c;
-                    *dst = fmaf(cum[i], inter[u], *dst);
+                    *dst = fmaf(ci, inter[u], *dst);
                 }
             }
         }
@@ -301,7 +306,7 @@ __global__ void __launch_bounds__(256) gated_inter_kernel(const RecArgs a, int c
         for (int r0 = r_lo; r0 < r_hi; r0 += 4) {
             float acc[4] = {0.f, 0.f, 0.f, 0.f};
             for (int j = 0; j < n; ++j) {
-                const float v = Vs[j * cols + c] * wj[j];
+                const float v = Vs[j * cols + c] * __shfl_sync(0xffffffffu, w_lane, j);
                 const float4 k = *reinterpret_cast<const float4*>(Ks + j * ldq + r0);
                 acc[0] = fmaf(k.x, v, acc[0]);
                 acc[1] = fmaf(k.y, v, acc[1]);
@@ -309,7 +314,7 @@ __global__ void __launch_bounds__(256) gated_inter_kernel(const RecArgs a, int c
                 acc[3] = fmaf(k.w, v, acc[3]);
             }
 #pragma unroll
-            for (int e = 0; e < 4; ++e) Ss[(r0 + e) * cols + c] = fmaf(cum[n - 1], Ss[(r0 + e) * cols + c], acc[e]);
+            for (int e = 0; e < 4; ++e) Ss[(r0 + e) * cols + c] = fmaf(cum_last, Ss[(r0 + e) * cols + c], acc[e]);
         }
     }
     __syncthreads();

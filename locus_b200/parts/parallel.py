@@ -3,6 +3,10 @@
 ``branches``: (name, mixer spec, factor) each; a branch's tensors live under ``<prefix>.<name>`` and the branch gets
 its factor as its ``out_scale``.  The branches share the layer's cache: at most one of them may keep pages and at most
 one a per-request state (the layer's cache entry has one of each).
+
+A branch behind the first that can run in two steps (``prepare``: all but its last product, on buffers and state of its
+own; ``finish``: the product that adds into the output) is prepared on the runtime's side stream while the first branch
+runs, and finished when both are done.
 """
 from __future__ import annotations
 
@@ -39,8 +43,17 @@ class ParallelMixers(Mixer):
         return [pl for b in self.branches for pl in b.step_plans()]
 
     def forward(self, h, batch, cache, residual, rt, accumulate=True) -> None:
+        early = {}
+        for i, b in enumerate(self.branches[1:], 1):
+            if hasattr(b, "prepare") and hasattr(b, "finish"):
+                with rt.side():
+                    early[i] = b.prepare(h, batch, cache, rt)
         for i, b in enumerate(self.branches):
-            if i == 0 and not accumulate and not b.can_overwrite:
+            if i in early:
+                if i == min(early):   # the side stream's work is done in order: one wait covers every branch on it
+                    rt.join()
+                b.finish(early[i], residual, rt, accumulate=True)
+            elif i == 0 and not accumulate and not b.can_overwrite:
                 residual.zero_()
                 b.forward(h, batch, cache, residual, rt)
             elif b.can_overwrite:

@@ -79,6 +79,11 @@ class StateSpace(Mixer):
                 (rt.max_tokens,), self.out_scale, dtype=torch.float32, device=rt.device))
 
     def forward(self, h, batch, cache, residual, rt, accumulate=True) -> None:
+        self.finish(self.prepare(h, batch, cache, rt), residual, rt, accumulate)
+
+    # The mixer in two steps, for a caller that runs it beside another mixer: everything up to the input of the output
+    # projection touches only this mixer's own buffers and state; the projection writes (or adds into) ``residual``.
+    def prepare(self, h, batch, cache, rt):
         T, H = batch.T, self.H
         proj = rt.rows("ssm.proj", self.width, torch.float32, T)
         K.linear(h, self.params["w_in"], proj)
@@ -104,6 +109,9 @@ class StateSpace(Mixer):
                            longest_new=longest)
         o = rt.rows("ssm.o", self.inner, rt.dtype, T)
         K.ssm_out(y, act, proj, 0, self.params["d_skip"], self.params["norm"], self.eps, o, parts=self.parts, v_dim=self.dv)
+        return o
+
+    def finish(self, o, residual, rt, accumulate=True) -> None:
         K.linear(o, self.params["w_o"], residual, accumulate=accumulate, row_scale=self._scale)
 
 
