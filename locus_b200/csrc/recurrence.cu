@@ -231,6 +231,7 @@ __global__ void __launch_bounds__(256) gated_inter_kernel(const RecArgs a, int c
     float* Ss = Vs + REC_CHUNK * cols;         // [d4][cols]
     float* kp = Ss + d4 * cols;                // [C] the chunk's keeps (1 behind its end)
     float* tk = kp + REC_CHUNK;                // [C] and takes (0 behind its end)
+    float* wj = tk + REC_CHUNK;                // [8 warps][C] take_j times the keeps behind j, every warp's own copy
     const int tid = threadIdx.x, lane = tid & 31, wid = tid >> 5;
     const int c = lane % cols, sub = lane / cols, nsub = 32 / cols;
     float* S = a.state + static_cast<size_t>(a.state_slots[seg]) * a.slot_stride + static_cast<size_t>(h) * d * dvx;
@@ -274,8 +275,10 @@ __global__ void __launch_bounds__(256) gated_inter_kernel(const RecArgs a, int c
             if (lane + o < 32) suf *= dn;
         }
         const float behind = __shfl_down_sync(0xffffffffu, suf, 1);
-        const float w_lane = tk[lane] * (lane < 31 ? behind : 1.f);
+        float* wj_w = wj + wid * REC_CHUNK;
+        wj_w[lane] = tk[lane] * (lane < 31 ? behind : 1.f);   // read below by lanes whose loops differ in length: no shuffles there
         const float cum_last = __shfl_sync(0xffffffffu, cum, n - 1);
+        __syncwarp();
         {   // o += c_i Q S: rows i = wid + 8 u, column c; the lanes' shares of the rows of S are summed by shuffles
             float inter[4] = {0.f, 0.f, 0.f, 0.f};
             for (int r4 = sub; r4 < d4 / 4; r4 += nsub) {
@@ -306,7 +309,7 @@ __global__ void __launch_bounds__(256) gated_inter_kernel(const RecArgs a, int c
         for (int r0 = r_lo; r0 < r_hi; r0 += 4) {
             float acc[4] = {0.f, 0.f, 0.f, 0.f};
             for (int j = 0; j < n; ++j) {
-                const float v = Vs[j * cols + c] * __shfl_sync(0xffffffffu, w_lane, j);
+                const float v = Vs[j * cols + c] * wj_w[j];
                 const float4 k = *reinterpret_cast<const float4*>(Ks + j * ldq + r0);
                 acc[0] = fmaf(k.x, v, acc[0]);
                 acc[1] = fmaf(k.y, v, acc[1]);
@@ -388,7 +391,7 @@ extern "C" int locus_gated_chunked(const float* q, int ldq, int off_q, const flo
     while (cols > 8 && static_cast<long long>(H) * ((a.dvx + cols - 1) / cols) * n_seg < 148) cols >>= 1;
     const int col_groups = (a.dvx + cols - 1) / cols;
     const size_t smem2 = sizeof(float) * (2 * REC_CHUNK * (d4 + 4) + REC_CHUNK * cols + static_cast<size_t>(d4) * cols +
-                                          2 * REC_CHUNK + 4);
+                                          10 * REC_CHUNK + 4);
     if (smem2 > 48 * 1024 &&
         cudaFuncSetAttribute(gated_inter_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, static_cast<int>(smem2)) !=
             cudaSuccess)
