@@ -4,6 +4,8 @@
     python -m locus_b200.tools.kernel_bench attn_decode --batch 8 --ctx 4000 [--heads 16 --kv-heads 16 --head-dim 128]
     python -m locus_b200.tools.kernel_bench attn_chunk --tokens 2048 --ctx 0
     python -m locus_b200.tools.kernel_bench experts --tokens 2048 [--experts 60 --top-k 4 --k 2048 --n 1408] [--part up|down]
+    python -m locus_b200.tools.kernel_bench recurrence --tokens 2048 --batch 1 [--heads 16 --head-dim 128 --v-dim 128]
+                                                       [--per-group 1] [--ones] [--retention]
 
 Times with CUDA events after warm-up.  Weights rotate through enough copies that the L2
 cannot hold them (``linear``); attention reads a cache larger than the L2 at the default
@@ -193,6 +195,47 @@ def bench_attn_chunk(args) -> None:
           f"{f'tcgen05, {n_splits} key ranges' if tc else (f'mma.sync, {n_splits} key ranges' if mma else 'cuda cores')}: {us:.1f} us/call  {flops / us / 1e6:.1f} TFLOP/s (causal flops)")
 
 
+def bench_recurrence(args) -> None:
+    """The gated linear recurrence over ``--batch`` requests of ``--tokens`` new tokens each (1: the token-by-token
+    kernel, as in a decode step; 16 and more: chunk by chunk), or with ``--retention`` the fixed-decay recurrence of the
+    same sizes beside it.  Bytes: the states read and written and the operands read; FLOPs: what the chunked form does
+    (a chunk's Q K^T and (Q K^T * D) V, Q S and the state's update) or, token by token, the update and S^T q."""
+    dev = "cuda:0"
+    B, n, H, d, dv, G = args.batch, args.tokens, args.heads, args.head_dim, args.v_dim, args.per_group
+    dvx = dv + (1 if args.ones else 0)
+    T = B * n
+    g = torch.Generator().manual_seed(1)
+    q0 = torch.arange(0, T, n, dtype=torch.int32, device=dev)
+    qn = torch.full((B,), n, dtype=torch.int32, device=dev)
+    slots = torch.arange(B, dtype=torch.int32, device=dev)
+    if args.retention:
+        rows = (torch.randn(T, 2 * H * d + 2 * H * dv, generator=g) * 0.3).to(dev)
+        state = torch.zeros(B, H, d, dv, device=dev)
+        decay = torch.full((H,), 0.99, device=dev)
+        out = torch.zeros(T, H * dv, device=dev)
+
+        def fn():
+            K.retention_scan(rows, state, slots, q0, qn, B, decay, d ** -0.5, out, n_heads=H, dim=d, v_dim=dv,
+                             short=n < K.RETENTION_CHUNK_FROM, long=n >= K.RETENTION_CHUNK_FROM, longest_new=n)
+    else:
+        Gn = H // G
+        rows = (torch.randn(T, 2 * Gn * d + H * dv, generator=g) * 0.3).to(dev)
+        keep = (torch.rand(T, H, generator=g) * 0.1 + 0.9).to(dev)
+        take = torch.rand(T, H, generator=g).to(dev)
+        state = torch.zeros(B, H * d * dvx, device=dev)
+        out = torch.zeros(T, H * dvx, device=dev)
+
+        def fn():
+            K.gated_recurrence(rows, 0, rows, Gn * d, rows, 2 * Gn * d, keep, take, state, 0, slots, q0, qn, B, out,
+                               n_heads=H, heads_per_group=G, dim=d, v_dim=dv, ones=args.ones,
+                               short=n < K.RECURRENCE_CHUNK_FROM, long=n >= K.RECURRENCE_CHUNK_FROM, longest_new=n)
+    us = _time(fn, args.iters, args.graph)
+    by = 4.0 * (2 * B * H * d * dvx + rows.numel() + out.numel())
+    fl = 2.0 * T * H * ((32 * d + 32 * dvx if n >= 16 else 0) + 2 * d * dvx)
+    print(f"{'retention' if args.retention else 'gated recurrence'}: {B} x {n} tokens, {H} heads of {d} x {dvx}: {us:.1f} us/call, "
+          f"{fl / us / 1e6:.2f} TFLOP/s (float32 FMA), {by / us / 1e3:.0f} GB/s")
+
+
 def bench_sample(args) -> None:
     """The sampling kernel on --rows rows of --vocab random float32 logits: greedy, temperature 0.8 alone, with
     top-k 50, with top-p 0.9, with top-k 50 + top-p 0.9 + min-p 0.05.  --one-block keeps every row on the one-block
@@ -215,7 +258,7 @@ def bench_sample(args) -> None:
 
 def main(argv=None) -> int:
     ap = argparse.ArgumentParser(prog="kernel_bench")
-    ap.add_argument("kernel", choices=["linear", "attn_decode", "attn_chunk", "experts", "sample"])
+    ap.add_argument("kernel", choices=["linear", "attn_decode", "attn_chunk", "experts", "sample", "recurrence"])
     ap.add_argument("--rows", type=int, default=8, help="sample: rows of logits")
     ap.add_argument("--vocab", type=int, default=151936, help="sample: logits of a row")
     ap.add_argument("--one-block", action="store_true", help="sample: never the cluster kernel")
@@ -233,6 +276,10 @@ def main(argv=None) -> int:
     ap.add_argument("--heads", type=int, default=16)
     ap.add_argument("--kv-heads", type=int, default=16)
     ap.add_argument("--head-dim", type=int, default=128)
+    ap.add_argument("--v-dim", type=int, default=128, help="recurrence: columns of a head's state")
+    ap.add_argument("--per-group", type=int, default=1, help="recurrence: heads that share q and k")
+    ap.add_argument("--ones", action="store_true", help="recurrence: one column more, whose v is 1")
+    ap.add_argument("--retention", action="store_true", help="recurrence: the fixed-decay kernels instead")
     ap.add_argument("--page-tokens", type=int, default=64)
     ap.add_argument("--window", type=int, default=0)
     ap.add_argument("--experts", type=int, default=60)
@@ -259,7 +306,7 @@ def main(argv=None) -> int:
         print("kernel_bench: no CUDA device", file=sys.stderr)
         return 1
     {"linear": bench_linear, "attn_decode": bench_attn_decode, "attn_chunk": bench_attn_chunk,
-     "experts": bench_experts, "sample": bench_sample}[args.kernel](args)
+     "experts": bench_experts, "sample": bench_sample, "recurrence": bench_recurrence}[args.kernel](args)
     return 0
 
 

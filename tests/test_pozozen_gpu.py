@@ -68,6 +68,44 @@ def test_other_page_sizes_and_the_cuda_core_products(page_tokens, dtype, cases, 
 
 
 @pytest.mark.parametrize("dtype", DTYPES, ids=["f32", "bf16"])
+@pytest.mark.parametrize("window", [0, 200])
+def test_heads_of_128_in_long_portions_on_pages_of_64(window, dtype, tmp_path_factory):
+    """Heads of 128 with grouped queries, portions of several hundred tokens (the kernels that long portions of that
+    head size take, with and without a window), states of 128 rows, pages of 64."""
+    from pozozen_cases import model, mlstm, moe, parallel, with_mlp
+
+    def tweak(name, w):
+        # a router as sharp as the small cases' turns the rounding of bfloat16 activations of this width into picks
+        # that flip at a few of 700 positions; the attention's scores stay sharp
+        sharpen(name, w)
+        for n in w:
+            if n.endswith(".router"):
+                w[n] = w[n] / 4.0
+
+    raw = model(256, 301, [with_mlp(parallel(4, 2, 128, 128, window, 4, 64, 128), moe(6, 2, 64, identity=2, groups=(4, 2), shared=64)),
+                           with_mlp(mlstm(2, 128, 64), None)], streams=2, loop=(0, 2, 2))
+    case = Case(f"big{window}", tmp_path_factory.mktemp("big"), torch.bfloat16, raw=raw, requests=(700, 90), tweak=tweak)
+    runner, cache = make_runner(case, dtype, "cuda:0", page_tokens=64, n_pages=20, max_tokens=640, max_seq=1024)
+    steps = [[("r0", 300), ("r1", 40)], [("r0", 399), ("r1", 1)], [("r0", 1), ("r1", 49)]]
+    got, routed = run_steps(runner, cache, case, steps)
+    if dtype == torch.float32:
+        compare(case, got, routed, *TOL[dtype], NEAR_TIE[dtype])
+        return
+    # bfloat16 at this width: the rounding of the activations shows at single positions where the matrix memory's
+    # normaliser n . q passes near zero or a router's choice nearly flips (measured: 2 or 3 of 700 positions between 3
+    # and 6 % of the largest logit, the mean error below 0.1 %, the same on the CUDA-core products), so the rows are
+    # judged together: the mean as everywhere, and all but one row in fifty within the tolerance
+    for rid, out in got.items():
+        ref = case.ref_following(rid, routed.get(rid), 0.1)
+        d = out - ref
+        d = d - d.mean(-1, keepdim=True)
+        top = float((ref - ref.mean(-1, keepdim=True)).abs().max())
+        err = d.abs().max(-1).values / top
+        assert float(d.abs().mean()) / top <= TOL[dtype][1] and float(err.max()) <= 0.15
+        assert int((err > TOL[dtype][0]).sum()) <= max(1, len(err) // 50), (rid, err.topk(5))
+
+
+@pytest.mark.parametrize("dtype", DTYPES, ids=["f32", "bf16"])
 def test_window_edges_in_prompts_and_in_decoding(dtype, tmp_path_factory):
     """A token that the rest of the sequence attends to strongly sits just inside the window of one query and just
     outside the next one's: the two logit rows must differ as the oracle's do.  The marker's key is made to stand out
