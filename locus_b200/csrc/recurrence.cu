@@ -228,8 +228,11 @@ __global__ void __launch_bounds__(256) gated_inter_kernel(const RecArgs a, int c
     float* Qs = rc_smem;                       // [C][ldq]
     float* Ks = Qs + REC_CHUNK * ldq;          // [C][ldq]
     float* Vs = Ks + REC_CHUNK * ldq;          // [C][cols]
-    float* Ss = Vs + REC_CHUNK * cols;         // [d4][cols]
-    float* kp = Ss + d4 * cols;                // [C] the chunk's keeps (1 behind its end)
+    // rows of the state lie lds floats apart: lanes of a warp that read the same column of rows 4 apart (the shares of
+    // the rows in Q S) or rows_o apart (the update) then hit different banks (cols 8: 10, cols 16: 20)
+    const int lds = cols == 32 ? 32 : cols + cols / 4;
+    float* Ss = Vs + REC_CHUNK * cols;         // [d4][lds]
+    float* kp = Ss + d4 * lds;                 // [C] the chunk's keeps (1 behind its end)
     float* tk = kp + REC_CHUNK;                // [C] and takes (0 behind its end)
     float* wj = tk + REC_CHUNK;                // [8 warps][C] take_j times the keeps behind j, every warp's own copy
     const int tid = threadIdx.x, lane = tid & 31, wid = tid >> 5;
@@ -237,7 +240,7 @@ __global__ void __launch_bounds__(256) gated_inter_kernel(const RecArgs a, int c
     float* S = a.state + static_cast<size_t>(a.state_slots[seg]) * a.slot_stride + static_cast<size_t>(h) * d * dvx;
     for (int i = tid; i < d4 * cols; i += 256) {
         const int r = i / cols, cc = i % cols;
-        Ss[i] = (r < d && c0 + cc < dvx) ? S[static_cast<size_t>(r) * dvx + c0 + cc] : 0.f;
+        Ss[r * lds + cc] = (r < d && c0 + cc < dvx) ? S[static_cast<size_t>(r) * dvx + c0 + cc] : 0.f;
     }
     const int g = h / a.heads_per_group;
     const int off_q = a.off_q + g * d, off_k = a.off_k + g * d, off_v = a.off_v + h * dv;
@@ -282,8 +285,8 @@ __global__ void __launch_bounds__(256) gated_inter_kernel(const RecArgs a, int c
         {   // o += c_i Q S: rows i = wid + 8 u, column c; the lanes' shares of the rows of S are summed by shuffles
             float inter[4] = {0.f, 0.f, 0.f, 0.f};
             for (int r4 = sub; r4 < d4 / 4; r4 += nsub) {
-                const float s0 = Ss[(4 * r4) * cols + c], s1 = Ss[(4 * r4 + 1) * cols + c];
-                const float s2 = Ss[(4 * r4 + 2) * cols + c], s3 = Ss[(4 * r4 + 3) * cols + c];
+                const float s0 = Ss[(4 * r4) * lds + c], s1 = Ss[(4 * r4 + 1) * lds + c];
+                const float s2 = Ss[(4 * r4 + 2) * lds + c], s3 = Ss[(4 * r4 + 3) * lds + c];
 #pragma unroll
                 for (int u = 0; u < 4; ++u) {
                     const float4 q = reinterpret_cast<const float4*>(Qs + (wid + 8 * u) * ldq)[r4];
@@ -317,13 +320,13 @@ __global__ void __launch_bounds__(256) gated_inter_kernel(const RecArgs a, int c
                 acc[3] = fmaf(k.w, v, acc[3]);
             }
 #pragma unroll
-            for (int e = 0; e < 4; ++e) Ss[(r0 + e) * cols + c] = fmaf(cum_last, Ss[(r0 + e) * cols + c], acc[e]);
+            for (int e = 0; e < 4; ++e) Ss[(r0 + e) * lds + c] = fmaf(cum_last, Ss[(r0 + e) * lds + c], acc[e]);
         }
     }
     __syncthreads();
     for (int i = tid; i < d4 * cols; i += 256) {
         const int r = i / cols, cc = i % cols;
-        if (r < d && c0 + cc < dvx) S[static_cast<size_t>(r) * dvx + c0 + cc] = Ss[i];
+        if (r < d && c0 + cc < dvx) S[static_cast<size_t>(r) * dvx + c0 + cc] = Ss[r * lds + cc];
     }
 }
 
@@ -390,7 +393,8 @@ extern "C" int locus_gated_chunked(const float* q, int ldq, int off_q, const flo
     int cols = 32;
     while (cols > 8 && static_cast<long long>(H) * ((a.dvx + cols - 1) / cols) * n_seg < 148) cols >>= 1;
     const int col_groups = (a.dvx + cols - 1) / cols;
-    const size_t smem2 = sizeof(float) * (2 * REC_CHUNK * (d4 + 4) + REC_CHUNK * cols + static_cast<size_t>(d4) * cols +
+    const int lds = cols == 32 ? 32 : cols + cols / 4;
+    const size_t smem2 = sizeof(float) * (2 * REC_CHUNK * (d4 + 4) + REC_CHUNK * cols + static_cast<size_t>(d4) * lds +
                                           10 * REC_CHUNK + 4);
     if (smem2 > 48 * 1024 &&
         cudaFuncSetAttribute(gated_inter_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, static_cast<int>(smem2)) !=
