@@ -87,32 +87,40 @@ extern "C" int locus_ssm_conv(const float* proj, int ld, int off_xbc, int off_dt
     return locus_launch_status();
 }
 
-// A warp per (token, part of the row).
-template <typename TO>
+// A group of GT threads per (token, part of the row): a warp for narrow parts, a block of 256 for wide ones.
+template <typename TO, int GT>
 __global__ void __launch_bounds__(256) ssm_out_kernel(const float* __restrict__ y, const float* __restrict__ act,
                                                       int channels, const float* __restrict__ proj, int ld, int off_z,
                                                       const void* __restrict__ dskip, int p_dt, const void* __restrict__ w,
                                                       int w_dt, float eps, TO* __restrict__ out, int n_units, int parts,
                                                       int inner, int dv) {
+    __shared__ float part_sum[8];
     pdl_entry();
     pdl_trigger();
-    const int lane = threadIdx.x & 31;
-    const int unit = blockIdx.x * 8 + (threadIdx.x >> 5);
-    if (unit >= n_units) return;
+    const int lane = threadIdx.x % GT;
+    const int unit = blockIdx.x * (256 / GT) + threadIdx.x / GT;
+    if (unit >= n_units) return;   // (a whole block at once when GT is 256)
     const int t = unit / parts, part = unit % parts, width = inner / parts, e0 = part * width;
     const float* yr = y + static_cast<size_t>(t) * inner;
     const float* xr = act + static_cast<size_t>(t) * channels;
     const float* zr = proj + static_cast<size_t>(t) * ld + off_z;
     float ss = 0.f;
-    for (int j = lane; j < width; j += 32) {
+    for (int j = lane; j < width; j += GT) {
         const int e = e0 + j;
         const float v = fmaf(ld_dyn(dskip, p_dt, e / dv), xr[e], yr[e]) * silu_f(zr[e]);
         ss = fmaf(v, v, ss);
     }
     ss = warp_sum(ss);
+    if (GT == 256) {
+        if ((threadIdx.x & 31) == 0) part_sum[threadIdx.x >> 5] = ss;
+        __syncthreads();
+        ss = 0.f;
+#pragma unroll
+        for (int k = 0; k < 8; ++k) ss += part_sum[k];
+    }
     const float scale = 1.0f / sqrtf(ss / static_cast<float>(width) + eps);
     TO* dst = out + static_cast<size_t>(t) * inner;
-    for (int j = lane; j < width; j += 32) {
+    for (int j = lane; j < width; j += GT) {
         const int e = e0 + j;
         const float v = fmaf(ld_dyn(dskip, p_dt, e / dv), xr[e], yr[e]) * silu_f(zr[e]);
         dst[e] = from_f<TO>(v * scale * ld_dyn(w, w_dt, e));
@@ -128,14 +136,18 @@ extern "C" int locus_ssm_out(const float* y, const float* act, int channels, con
     if (parts <= 0 || inner <= 0 || inner % parts || dv <= 0 || inner % dv) return LOCUS_ERR_UNSUPPORTED;
     const long long units = static_cast<long long>(T) * parts;
     if (units > 0x7fffffffLL) return LOCUS_ERR_UNSUPPORTED;
-    const int blocks = static_cast<int>((units + 7) / 8), n = static_cast<int>(units);
-    if (out_dt == LOCUS_DT_BF16)
-        locus_launch(ssm_out_kernel<bf16>, blocks, 256, 0, stream, y, act, channels, proj, ld, off_z, dskip, p_dt, w, w_dt,
-                     eps, static_cast<bf16*>(out), n, parts, inner, dv);
-    else if (out_dt == LOCUS_DT_F32)
-        locus_launch(ssm_out_kernel<float>, blocks, 256, 0, stream, y, act, channels, proj, ld, off_z, dskip, p_dt, w, w_dt,
-                     eps, static_cast<float*>(out), n, parts, inner, dv);
-    else
+    const bool wide = inner / parts >= 1024;
+    const int n = static_cast<int>(units), blocks = wide ? n : static_cast<int>((units + 7) / 8);
+#define SSM_OUT(TO, GT)                                                                                              \
+    locus_launch(ssm_out_kernel<TO, GT>, blocks, 256, 0, stream, y, act, channels, proj, ld, off_z, dskip, p_dt, w, w_dt, \
+                 eps, static_cast<TO*>(out), n, parts, inner, dv)
+    if (out_dt == LOCUS_DT_BF16) {
+        if (wide) SSM_OUT(bf16, 256); else SSM_OUT(bf16, 32);
+    } else if (out_dt == LOCUS_DT_F32) {
+        if (wide) SSM_OUT(float, 256); else SSM_OUT(float, 32);
+    } else {
         return LOCUS_ERR_UNSUPPORTED;
+    }
+#undef SSM_OUT
     return locus_launch_status();
 }

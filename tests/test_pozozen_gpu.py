@@ -252,7 +252,8 @@ def test_mlstm_gates_and_output_stage_against_their_twins(heads, v_dim):
 
 
 @pytest.mark.parametrize("wdt", DTYPES, ids=["f32", "bf16"])
-@pytest.mark.parametrize("heads,v_dim,state,groups,taps,parts", [(4, 8, 16, 2, 4, 2), (3, 5, 9, 3, 5, 3), (2, 40, 72, 1, 1, 1), (1, 11, 7, 1, 2, 1)])
+@pytest.mark.parametrize("heads,v_dim,state,groups,taps,parts", [(4, 8, 16, 2, 4, 2), (3, 5, 9, 3, 5, 3), (2, 40, 72, 1, 1, 1), (1, 11, 7, 1, 2, 1),
+                                                                   (16, 64, 8, 1, 4, 1), (20, 64, 4, 1, 2, 1)])
 def test_state_space_kernels_against_their_twins(heads, v_dim, state, groups, taps, parts, wdt):
     """The convolution over portions that are shorter and longer than its reach (in one launch and cut in two, the
     inputs handed on through the slot), the gates, and the output stage."""
