@@ -106,6 +106,21 @@ def test_heads_of_128_in_long_portions_on_pages_of_64(window, dtype, tmp_path_fa
 
 
 @pytest.mark.parametrize("dtype", DTYPES, ids=["f32", "bf16"])
+@pytest.mark.parametrize("dim,window", [(64, 40), (128, 0)])
+def test_four_requests_decode_side_by_side_with_grouped_queries(dim, window, dtype, tmp_path_factory):
+    """Heads of 64 and 128, four query heads on every key/value head, four requests that decode together (the decode
+    kernel that serves a whole group of query heads from one pass over the keys), past a window whose pages go back."""
+    from pozozen_cases import model, mlstm, parallel, with_mlp
+
+    raw = model(128, 150, [with_mlp(parallel(16, 4, dim, dim, window, 2, 32, 16), None), with_mlp(mlstm(1, 32, 32), None)], streams=2)
+    case = Case(f"gq{dim}", tmp_path_factory.mktemp("gq"), torch.bfloat16, raw=raw, requests=(90, 75, 80, 64))
+    runner, cache = make_runner(case, dtype, "cuda:0", page_tokens=16, n_pages=30, max_tokens=128)
+    steps = [[("r0", 30), ("r1", 15), ("r2", 20), ("r3", 4)]] + [[("r0", 1), ("r1", 1), ("r2", 1), ("r3", 1)]] * 60
+    got, routed = run_steps(runner, cache, case, steps)
+    compare(case, got, routed, *TOL[dtype], NEAR_TIE[dtype])
+
+
+@pytest.mark.parametrize("dtype", DTYPES, ids=["f32", "bf16"])
 def test_window_edges_in_prompts_and_in_decoding(dtype, tmp_path_factory):
     """A token that the rest of the sequence attends to strongly sits just inside the window of one query and just
     outside the next one's: the two logit rows must differ as the oracle's do.  The marker's key is made to stand out
