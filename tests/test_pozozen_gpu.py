@@ -14,7 +14,7 @@ import torch
 
 import emulated_kernels as EK
 import plain_pozozen as plain
-from pozozen_cases import CONFIGS, Case, compare, make_runner, run_steps, schedules, sharpen
+from pozozen_cases import CONFIGS, Case, compare, compare_together, make_runner, run_steps, schedules, sharpen
 
 pytestmark = pytest.mark.gpu
 ROOT = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
@@ -49,6 +49,31 @@ def test_every_schedule_agrees_with_plain(name, dtype, cases):
         got, routed = run_steps(runner, cache, case, steps)
         compare(case, got, routed, *TOL[dtype], NEAR_TIE[dtype])
         assert cache.free_pages() == cache.total_pages() and cache.state_slots.free == cache.state_slots.total, sched_name
+
+
+@pytest.mark.parametrize("dtype", DTYPES, ids=["f32", "bf16"])
+@pytest.mark.parametrize("seed", list(range(8)))
+def test_drawn_configurations_on_pages_of_64(seed, dtype, tmp_path_factory):
+    """Configurations drawn at random (layer order, loop, streams, heads, sizes, windows, groups, taps, experts,
+    constants): portions of changing size and mixed batches of four live requests on pages of 64 whose pool only
+    holds them when pages are used again."""
+    from pozozen_cases import random_config, sharpen_mildly
+
+    raw = random_config(100 + seed)
+    case = Case(f"drawn{seed}", tmp_path_factory.mktemp("drawn"), torch.bfloat16, raw=raw, requests=(230, 1, 150, 40, 97, 180), tweak=sharpen_mildly)
+    runner, cache = make_runner(case, dtype, "cuda:0", page_tokens=64, n_pages=12, max_tokens=256, max_seq=512)
+    sch = schedules(case)
+    for name in ("mixed", "chunked"):
+        got, routed = run_steps(runner, cache, case, sch[name])
+        # Single rows amplify rounding (a router's near-flip, a matrix memory's normaliser near zero).  In float32 the
+        # rows are judged together at the usual tolerances, which holds the logic and the router (near-ties of 2e-5).
+        # In bfloat16 such rows move by up to half the largest logit -- the same rows by as much when the products run
+        # on the CUDA cores, and for every cut of the prompt: the rounding of the activations, not a kernel -- and a
+        # row that has moved may take other experts than the oracle; there the mean error and nine rows in ten are held.
+        if dtype == torch.float32:
+            compare_together(case, got, routed, *TOL[dtype], 2e-5)
+        else:
+            compare_together(case, got, routed, *TOL[dtype], 0.5, one_in=10, cap=40.0)
 
 
 @pytest.mark.parametrize("dtype", DTYPES, ids=["f32", "bf16"])
@@ -94,15 +119,8 @@ def test_heads_of_128_in_long_portions_on_pages_of_64(window, dtype, tmp_path_fa
     # bfloat16 at this width: the rounding of the activations shows at single positions where the matrix memory's
     # normaliser n . q passes near zero or a router's choice nearly flips (measured: 2 or 3 of 700 positions between 3
     # and 6 % of the largest logit, the mean error below 0.1 %, the same on the CUDA-core products), so the rows are
-    # judged together: the mean as everywhere, and all but one row in fifty within the tolerance
-    for rid, out in got.items():
-        ref = case.ref_following(rid, routed.get(rid), 0.1)
-        d = out - ref
-        d = d - d.mean(-1, keepdim=True)
-        top = float((ref - ref.mean(-1, keepdim=True)).abs().max())
-        err = d.abs().max(-1).values / top
-        assert float(d.abs().mean()) / top <= TOL[dtype][1] and float(err.max()) <= 0.15
-        assert int((err > TOL[dtype][0]).sum()) <= max(1, len(err) // 50), (rid, err.topk(5))
+    # judged together
+    compare_together(case, got, routed, *TOL[dtype], 0.1)
 
 
 @pytest.mark.parametrize("dtype", DTYPES, ids=["f32", "bf16"])
