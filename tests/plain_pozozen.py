@@ -1,7 +1,7 @@
 """A plain, slow, whole-sequence implementation of the Pozozen design: one function per mechanism,
 float64 on the CPU, written from the design's equations and sharing no code with the engine.
 
-The design: a decoder with ``streams`` copies of the residual stream ("hyper-connections").  A sublayer
+The design: a decoder with ``streams`` copies of the residual stream.  A sublayer
 (mixer, then feed-forward) reads a weighted sum of the streams through a layer norm with weight and bias, and
 its output is written back into every stream while the streams are mixed among themselves:
 
